@@ -1,0 +1,150 @@
+/*
+ * nvllm_b200 — C ABI of the paged-attention path for nano-vllm on NVIDIA B200 (sm_100a).
+ *
+ * The library replaces the three device operations behind nano-vllm's attention layer
+ * (nanovllm/layers/attention.py): the Triton `store_kvcache_kernel`, the
+ * `flash_attn_varlen_func` prefill call and the `flash_attn_with_kvcache` decode call.
+ *
+ * Conventions shared by every entry point
+ *   - All tensors are bf16 (2-byte elements); metadata is int32.  Strides and extents are in
+ *     ELEMENTS, never bytes.  Every data pointer and every row stride must be 16-byte aligned
+ *     (8 elements); an entry point rejects anything else instead of taking a slow path.
+ *   - The caller owns every buffer.  No entry point allocates, frees or synchronises, and
+ *     every kernel is launched on the `stream` that is passed in (a `cudaStream_t` given as
+ *     `void*`; NULL is the legacy default stream), on the device that is current.  That makes
+ *     every launch legal inside CUDA stream capture.
+ *   - Launch geometry depends only on host-visible arguments (batch, table width, head
+ *     counts), never on device-resident lengths, so a captured graph can be replayed with
+ *     new `context_lens` / `block_tables` / `slot_mapping` contents.
+ *   - Return value: 0 = kernels launched; a negative NVLLM_E_* code = the arguments were
+ *     rejected on the host before any launch.  `nvllm_last_error()` then holds a message.
+ *     No C++ exception crosses this boundary.
+ *   - Problems that only the device can see (a slot or block id outside the cache) never
+ *     trap: the offending access is skipped and a bit is set in a device status word that
+ *     `nvllm_read_status()` returns.
+ *
+ * KV-cache layout (nanovllm/engine/model_runner.py:136-149): one plane per layer for K and
+ * one for V, each `[num_blocks, 256, Hkv, D]` contiguous.  Flat slot s = block*256 + offset;
+ * element (s, h, d) sits at s*Hkv*D + h*D + d.
+ */
+#ifndef NVLLM_B200_H_
+#define NVLLM_B200_H_
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define NVLLM_API __attribute__((visibility("default")))
+#else
+#define NVLLM_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NVLLM_BLOCK_SIZE 256 /* tokens per KV-cache block (nanovllm/engine/sequence.py:15) */
+
+/* host-side rejection codes */
+#define NVLLM_OK 0
+#define NVLLM_E_NULL (-1)      /* a required pointer is NULL */
+#define NVLLM_E_ALIGN (-2)     /* pointer or stride not 16-byte aligned */
+#define NVLLM_E_GEOMETRY (-3)  /* unsupported head_dim / head counts / sizes */
+#define NVLLM_E_WORKSPACE (-4) /* decode workspace missing or too small */
+#define NVLLM_E_CUDA (-5)      /* the CUDA runtime refused the launch */
+#define NVLLM_E_NO_DEVICE (-6) /* no usable sm_100 device is current */
+
+/* bits of the device status word */
+#define NVLLM_STATUS_BAD_SLOT 1  /* store_kvcache saw slot >= num_slots (row skipped) */
+#define NVLLM_STATUS_BAD_BLOCK 2 /* a block_tables entry in use was outside [0,num_blocks) */
+
+/*
+ * Scatter the new tokens' K and V rows into the paged cache.
+ * Replaces store_kvcache_kernel + store_kvcache (nanovllm/layers/attention.py:10-39):
+ *   k_cache_flat[slot_mapping[i]] = key[i], same for V; a row is row_elems = Hkv*D elements.
+ * key/value: [n_tokens, row_elems] with unit inner stride and the given row strides (value
+ * is a strided view of the fused qkv activation in the caller).  Rows with slot < 0 are
+ * skipped; rows with slot >= num_slots are skipped and flagged.  Pure copy: bit-exact.
+ */
+NVLLM_API int nvllm_store_kvcache(const void* key, int64_t key_row_stride,
+                        const void* value, int64_t value_row_stride,
+                        void* k_cache, void* v_cache,
+                        const int32_t* slot_mapping, int64_t n_tokens,
+                        int32_t row_elems, int64_t num_slots, void* stream);
+
+/*
+ * Paged GQA decode: one query token per sequence against context_lens[b] cached tokens.
+ * Replaces the flash_attn_with_kvcache call (nanovllm/layers/attention.py:74-77).
+ *   out[b,h,:] = sum_{t<ctx_b} softmax_t(scale * q[b,h].K[t,h/G]) V[t,h/G],  G = Hq/Hkv.
+ * q/out: [batch, Hq, D] with unit inner strides and the given row (per sequence) strides.
+ * block_tables: [batch, max_blocks] int32 with row stride bt_row_stride; only the first
+ * ceil(ctx_b/256) entries of a row are read.  ctx_b == 0 gives a zero output row and
+ * touches no cache memory.  Long contexts are cut into chunks handled by separate thread
+ * blocks (split-KV) whose fp32 partial results go through `workspace` and are merged by a
+ * second kernel; `workspace` must hold nvllm_decode_workspace_bytes(...) bytes for the
+ * same (batch, max_blocks, Hq, Hkv, D) and is scratch (no state is kept between calls).
+ * Supported: D in {64,128}; Hq % Hkv == 0; G <= 8.
+ */
+NVLLM_API int nvllm_decode_paged(const void* q, int64_t q_row_stride,
+                       const void* k_cache, const void* v_cache,
+                       const int32_t* context_lens,
+                       const int32_t* block_tables, int64_t bt_row_stride, int32_t max_blocks,
+                       void* out, int64_t out_row_stride,
+                       int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                       float scale, int64_t num_blocks,
+                       void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Bytes of scratch nvllm_decode_paged needs for this geometry (0 if no split is used).
+ * Negative NVLLM_E_* on unsupported geometry.  Pure host arithmetic.
+ * No counterpart in the reference: flash-attn allocates its split-KV scratch internally. */
+NVLLM_API int64_t nvllm_decode_workspace_bytes(int32_t batch, int32_t max_blocks,
+                                     int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim);
+
+/* The split-KV plan the library uses for this geometry: tokens per chunk and the maximum
+ * number of chunks per sequence.  Pure host arithmetic, exposed for tests and reports. */
+NVLLM_API int nvllm_decode_plan(int32_t batch, int32_t max_blocks, int32_t num_q_heads,
+                      int32_t num_kv_heads, int32_t head_dim,
+                      int32_t* chunk_tokens, int32_t* max_splits);
+
+/*
+ * Varlen causal GQA prefill.  Replaces the flash_attn_varlen_func call
+ * (nanovllm/layers/attention.py:67-73).  For sequence b, query row i (0-based among its
+ * Lq_b = cu_seqlens_q[b+1]-cu_seqlens_q[b] new tokens) attends keys j <= i + (Lk_b - Lq_b),
+ * j over the full sequence of Lk_b = cu_seqlens_k[b+1]-cu_seqlens_k[b] tokens
+ * (bottom-right aligned causal mask).  Two K/V sources:
+ *   - packed (block_tables == NULL): key j of sequence b is row cu_seqlens_k[b]+j of
+ *     k / v, each [total_k, Hkv, D] with the given row strides;
+ *   - paged (block_tables != NULL): k / v are the cache planes and key j of sequence b is
+ *     slot block_tables[b, j/256]*256 + j%256; the k/v row strides are ignored.
+ * q/out: [total_q, Hq, D] with the given row strides.  Lq_b == 0 is legal (no work).
+ * Supported: D in {64,128}; Hq % Hkv == 0.
+ */
+NVLLM_API int nvllm_prefill_varlen(const void* q, int64_t q_row_stride,
+                         const void* k, int64_t k_row_stride,
+                         const void* v, int64_t v_row_stride,
+                         const int32_t* block_tables, int64_t bt_row_stride, int32_t max_blocks,
+                         void* out, int64_t out_row_stride,
+                         const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                         int32_t batch, int32_t max_seqlen_q, int32_t max_seqlen_k,
+                         int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                         float scale, int64_t num_blocks, void* stream);
+
+/* Message for the last negative return value on this thread ("" if none).
+ * No counterpart in the reference (it raises Python exceptions). */
+NVLLM_API const char* nvllm_last_error(void);
+
+/* Copies the current device's status word to *host_out and clears it.  Synchronises the
+ * device: call it between steps, never during stream capture.  Returns 0 or NVLLM_E_*.
+ * No counterpart in the reference. */
+NVLLM_API int nvllm_read_status(int32_t* host_out);
+
+/* ABI version of this header (bumped on any signature change). */
+NVLLM_API int nvllm_abi_version(void);
+
+/* How many kernels this library has launched in this process (all entry points, all
+ * devices).  Monotonic; used by the benchmark to report its launch count. */
+NVLLM_API int64_t nvllm_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVLLM_B200_H_ */

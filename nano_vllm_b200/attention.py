@@ -1,0 +1,200 @@
+"""Attention layer of nano-vllm on the B200 kernels: the host side of the C ABI.
+
+Same surface as nanovllm/layers/attention.py:32-79 — ``store_kvcache(key, value, k_cache,
+v_cache, slot_mapping)`` and ``Attention(num_heads, head_dim, scale, num_kv_heads)`` with the
+``k_cache`` / ``v_cache`` attributes that the model runner binds
+(nanovllm/engine/model_runner.py:145-149) and ``forward(q, k, v)`` driven by the per-step
+context — but every device operation goes through libnvllm_b200.so.  Tensors must live on a
+CUDA device and be bf16; anything else raises (there is no CPU or eager fallback).
+"""
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+from torch import nn
+
+from . import _lib
+from . import context as _own_context
+
+BLOCK_SIZE = 256
+
+_get_context: Callable[[], object] = _own_context.get_context
+
+
+def use_context_getter(getter: Callable[[], object]) -> None:
+    """Makes ``Attention.forward`` read its metadata from another module's ``get_context``
+    (nano-vllm's ``nanovllm.utils.context.get_context`` when running inside that engine)."""
+    global _get_context
+    _get_context = getter
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _require_cuda_bf16(name: str, t: torch.Tensor) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (nano_vllm_b200 has no CPU path)")
+    if t.dtype != torch.bfloat16:
+        raise RuntimeError(f"{name} must be bfloat16, got {t.dtype}")
+
+
+def _require_i32(name: str, t: torch.Tensor) -> None:
+    if not t.is_cuda or t.dtype != torch.int32 or (t.dim() > 0 and t.stride(-1) != 1):
+        raise RuntimeError(f"{name} must be a CUDA int32 tensor with unit inner stride")
+
+
+# ---- decode scratch ---------------------------------------------------------------------
+# One buffer per device, grown on demand.  Outgrown buffers are kept alive because CUDA
+# graphs captured earlier still hold their addresses.
+_workspaces: dict[int, torch.Tensor] = {}
+_retired: list[torch.Tensor] = []
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor | None:
+    if nbytes == 0:
+        return None
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(idx)
+    if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _retired.append(ws)
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[idx] = ws
+    return ws
+
+
+# ---- functional entry points ------------------------------------------------------------
+
+def store_kvcache(key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  slot_mapping: torch.Tensor) -> None:
+    """k_cache.view(-1, Hkv*D)[slot_mapping[i]] = key[i] (same for value); bit-exact copy.
+
+    Same argument contract and asserts as nanovllm/layers/attention.py:32-39.
+    """
+    N, num_heads, head_dim = key.shape
+    D = num_heads * head_dim
+    assert key.stride(-1) == 1 and value.stride(-1) == 1
+    assert key.stride(1) == head_dim and value.stride(1) == head_dim
+    assert k_cache.stride(1) == D and v_cache.stride(1) == D
+    assert slot_mapping.numel() == N
+    for name, t in (("key", key), ("value", value), ("k_cache", k_cache), ("v_cache", v_cache)):
+        _require_cuda_bf16(name, t)
+    _require_i32("slot_mapping", slot_mapping)
+    num_slots = k_cache.numel() // D
+    with torch.cuda.device(key.device):
+        _lib.check(_lib.load().nvllm_store_kvcache(
+            key.data_ptr(), key.stride(0), value.data_ptr(), value.stride(0),
+            k_cache.data_ptr(), v_cache.data_ptr(), slot_mapping.data_ptr(),
+            N, D, num_slots, _stream(key)))
+
+
+def decode_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, context_lens: torch.Tensor,
+                 block_tables: torch.Tensor, scale: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One query token per sequence against the paged cache; q/out are ``[B, Hq, D]``.
+
+    Stands where ``flash_attn_with_kvcache(q.unsqueeze(1), k_cache, v_cache,
+    cache_seqlens=context_lens, block_table=block_tables, softmax_scale=scale, causal=True)``
+    stands in nanovllm/layers/attention.py:74-77.
+    """
+    B, Hq, D = q.shape
+    Hkv = k_cache.shape[-2]
+    _require_cuda_bf16("q", q)
+    _require_cuda_bf16("k_cache", k_cache)
+    _require_cuda_bf16("v_cache", v_cache)
+    _require_i32("context_lens", context_lens)
+    _require_i32("block_tables", block_tables)
+    assert q.stride(-1) == 1 and q.stride(1) == D
+    assert k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert block_tables.dim() == 2 and block_tables.shape[0] == B and context_lens.numel() == B
+    if out is None:
+        out = torch.empty((B, Hq, D), dtype=q.dtype, device=q.device)
+    assert out.stride(-1) == 1 and out.stride(1) == D
+    max_blocks = block_tables.shape[1]
+    num_blocks = k_cache.numel() // (BLOCK_SIZE * Hkv * D)
+    if B == 0:
+        return out
+    with torch.cuda.device(q.device):
+        ws = _workspace(q.device, _lib.decode_workspace_bytes(B, max_blocks, Hq, Hkv, D))
+        _lib.check(_lib.load().nvllm_decode_paged(
+            q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+            context_lens.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), max_blocks,
+            out.data_ptr(), out.stride(0), B, Hq, Hkv, D, float(scale), num_blocks,
+            ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, _stream(q)))
+    return out
+
+
+def prefill_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: torch.Tensor,
+                   cu_seqlens_k: torch.Tensor, max_seqlen_q: int, max_seqlen_k: int, scale: float,
+                   block_tables: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Varlen causal GQA attention over packed K/V rows, or over the paged cache when
+    ``block_tables`` is given (then ``k``/``v`` are the cache planes).  q/out: ``[N, Hq, D]``.
+
+    Stands where ``flash_attn_varlen_func(..., causal=True, block_table=block_tables)`` stands
+    in nanovllm/layers/attention.py:70-73.
+    """
+    N, Hq, D = q.shape
+    Hkv = k.shape[-2]
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _require_cuda_bf16(name, t)
+    _require_i32("cu_seqlens_q", cu_seqlens_q)
+    _require_i32("cu_seqlens_k", cu_seqlens_k)
+    assert q.stride(-1) == 1 and q.stride(1) == D
+    batch = cu_seqlens_q.numel() - 1
+    assert cu_seqlens_k.numel() == batch + 1
+    if out is None:
+        out = torch.empty((N, Hq, D), dtype=q.dtype, device=q.device)
+    assert out.stride(-1) == 1 and out.stride(1) == D
+    if block_tables is not None:
+        _require_i32("block_tables", block_tables)
+        assert k.is_contiguous() and v.is_contiguous() and k.dim() == 4 and k.shape[1] == BLOCK_SIZE
+        assert block_tables.dim() == 2 and block_tables.shape[0] == batch
+        bt_ptr, bt_stride, max_blocks = block_tables.data_ptr(), block_tables.stride(0), block_tables.shape[1]
+        num_blocks = k.shape[0]
+        k_stride = v_stride = Hkv * D
+    else:
+        assert k.dim() == 3 and k.stride(-1) == 1 and v.stride(-1) == 1 and k.stride(1) == D and v.stride(1) == D
+        bt_ptr, bt_stride, max_blocks, num_blocks = None, 0, 0, 0
+        k_stride, v_stride = k.stride(0), v.stride(0)
+    if N == 0 or batch == 0:
+        return out
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.load().nvllm_prefill_varlen(
+            q.data_ptr(), q.stride(0), k.data_ptr(), k_stride, v.data_ptr(), v_stride,
+            bt_ptr, bt_stride, max_blocks, out.data_ptr(), out.stride(0),
+            cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), batch, int(max_seqlen_q), int(max_seqlen_k),
+            Hq, Hkv, D, float(scale), num_blocks, _stream(q)))
+    return out
+
+
+# ---- the layer --------------------------------------------------------------------------
+
+class Attention(nn.Module):
+    """Drop-in for nanovllm/layers/attention.py:42-79 (same constructor, attributes, forward)."""
+
+    def __init__(self, num_heads, head_dim, scale, num_kv_heads):
+        super().__init__()
+        self.num_heads = num_heads
+        self.head_dim = head_dim
+        self.scale = scale
+        self.num_kv_heads = num_kv_heads
+        self.k_cache = self.v_cache = torch.tensor([])
+
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
+        q = q.view(-1, self.num_heads, self.head_dim)
+        k = k.view(-1, self.num_kv_heads, self.head_dim)
+        v = v.view(-1, self.num_kv_heads, self.head_dim)
+        context = _get_context()
+        k_cache, v_cache = self.k_cache, self.v_cache
+        if k_cache.numel() and v_cache.numel():
+            store_kvcache(k, v, k_cache, v_cache, context.slot_mapping)
+        if context.is_prefill:
+            if context.block_tables is not None:  # prefix cache: read every key through the table
+                k, v = k_cache, v_cache
+            o = prefill_varlen(q, k, v, context.cu_seqlens_q, context.cu_seqlens_k,
+                               context.max_seqlen_q, context.max_seqlen_k, self.scale,
+                               block_tables=context.block_tables)
+        else:
+            o = decode_paged(q, k_cache, v_cache, context.context_lens, context.block_tables, self.scale)
+        return o.view(-1, self.num_heads * self.head_dim)

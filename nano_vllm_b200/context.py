@@ -1,0 +1,44 @@
+"""Per-step attention metadata, the input contract of the attention layer.
+
+Field for field the same carrier as nanovllm/utils/context.py:5-27: the model runner fills it
+before every forward (prepare_prefill / prepare_decode in nanovllm/engine/model_runner.py:161-249)
+and the attention layer reads it.  When this package is installed into nano-vllm the
+runner's own module is used instead (see ``attention.use_context_getter``); this copy lets the
+attention layer run and be tested without the engine.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+
+@dataclass
+class Context:
+    is_prefill: bool = False
+    cu_seqlens_q: torch.Tensor | None = None
+    cu_seqlens_k: torch.Tensor | None = None
+    max_seqlen_q: int = 0
+    max_seqlen_k: int = 0
+    slot_mapping: torch.Tensor | None = None
+    context_lens: torch.Tensor | None = None
+    block_tables: torch.Tensor | None = None
+
+
+_CONTEXT = Context()
+
+
+def get_context() -> Context:
+    return _CONTEXT
+
+
+def set_context(is_prefill, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=0, max_seqlen_k=0,
+                slot_mapping=None, context_lens=None, block_tables=None) -> None:
+    global _CONTEXT
+    _CONTEXT = Context(is_prefill, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
+                       slot_mapping, context_lens, block_tables)
+
+
+def reset_context() -> None:
+    global _CONTEXT
+    _CONTEXT = Context()

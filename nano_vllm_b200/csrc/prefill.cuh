@@ -1,0 +1,31 @@
+// Parameters shared by the prefill kernels and their host-side dispatcher.
+#pragma once
+#include "common.cuh"
+
+namespace nvllm {
+
+struct PrefillParams {
+  const __nv_bfloat16* q;
+  int64_t q_stride;
+  const __nv_bfloat16* k;  // packed K rows, or the K cache plane when block_tables != nullptr
+  int64_t k_stride;
+  const __nv_bfloat16* v;
+  int64_t v_stride;
+  const int32_t* block_tables;  // nullptr = packed K/V
+  int64_t bt_stride;
+  int max_blocks;
+  __nv_bfloat16* out;
+  int64_t out_stride;
+  const int32_t* cu_q;
+  const int32_t* cu_k;
+  int batch, max_seqlen_q, max_seqlen_k;
+  int hq, hkv, g, d;
+  float scale_log2e;
+  int64_t num_blocks;
+  int* status;
+};
+
+// Warp-level mma.sync kernel: every supported geometry.
+int launch_prefill_mma(const PrefillParams& p, cudaStream_t stream);
+
+}  // namespace nvllm

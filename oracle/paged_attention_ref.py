@@ -1,0 +1,112 @@
+"""CPU restatement of nano-vllm's attention path — TEST INFRASTRUCTURE, not product code.
+
+What it restates (reference file:line):
+  * store_kvcache      — nanovllm/layers/attention.py:10-39: cache row slot_mapping[i] of the
+    flattened ``[num_slots, Hkv*D]`` plane receives key[i] / value[i].
+  * Attention.forward  — nanovllm/layers/attention.py:58-79: store first, then either the
+    varlen causal prefill (packed K/V, or the cache read through block_tables when a prefix
+    was cached) or the paged decode.
+The attention arithmetic itself lives in the third-party flash-attn wheel (declared unpinned
+in the reference's pyproject.toml:18; 2.8.3 in this image), which is not part of the
+reference tree.  Its published semantics are restated here: fp32
+``softmax(scale * Q K^T + mask) V`` with query head h reading KV head h // (Hq/Hkv), causal
+mask aligned to the bottom-right corner (query i of Lq sees keys j <= i + Lk - Lq), rows with
+no visible key giving zeros, paged K/V ``[num_blocks, 256, Hkv, D]`` addressed through an
+int32 block table.  Arithmetic: bf16 inputs upcast to fp32,
+``torch.nn.functional.scaled_dot_product_attention`` on the host.
+
+Pinning: the reference has no tests or golden vectors for this path.  The oracle is pinned
+by tests/golden/*.npz, which hold outputs of the reference's own ``Attention.forward`` and
+``store_kvcache`` (Triton + flash-attn) recorded on a B200 by tests/golden/make_golden.py;
+tests/test_oracle_golden.py checks this file against them.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+BLOCK_SIZE = 256
+
+
+def store_kvcache_ref(key, value, k_cache, v_cache, slot_mapping):
+    """In-place scatter on CPU tensors; rows with a negative slot are skipped (the Triton
+    kernel of the reference has no such rows; the runner never emits them)."""
+    n = key.shape[0]
+    if n == 0 or k_cache.numel() == 0:
+        return
+    row = key.shape[1] * key.shape[2]
+    slots = slot_mapping.to(torch.int64)
+    keep = slots >= 0
+    kf = k_cache.view(-1, row)
+    vf = v_cache.view(-1, row)
+    kf[slots[keep]] = key.reshape(n, row)[keep]
+    vf[slots[keep]] = value.reshape(n, row)[keep]
+
+
+def gather_paged(cache, block_table_row, length):
+    """[length, Hkv, D] view of one sequence's tokens, in order, through its block table."""
+    nblk = (length + BLOCK_SIZE - 1) // BLOCK_SIZE
+    ids = block_table_row[:nblk].to(torch.int64)
+    return cache[ids].reshape(nblk * BLOCK_SIZE, cache.shape[2], cache.shape[3])[:length]
+
+
+def _sdpa(q, k, v, scale, mask=None):
+    # q [Lq,Hq,D], k/v [Lk,Hkv,D] -> [Lq,Hq,D], fp32
+    qf = q.float().transpose(0, 1).unsqueeze(0)
+    kf = k.float().transpose(0, 1).unsqueeze(0)
+    vf = v.float().transpose(0, 1).unsqueeze(0)
+    o = F.scaled_dot_product_attention(qf, kf, vf, attn_mask=mask, scale=scale, enable_gqa=True)
+    return o.squeeze(0).transpose(0, 1)
+
+
+def decode_ref(q, k_cache, v_cache, context_lens, block_tables, scale):
+    """q [B,Hq,D] -> fp32 [B,Hq,D]; sequences with context_len 0 give zeros."""
+    B = q.shape[0]
+    out = torch.zeros(q.shape, dtype=torch.float32)
+    for b in range(B):
+        n = int(context_lens[b])
+        if n <= 0:
+            continue
+        k = gather_paged(k_cache, block_tables[b], n)
+        v = gather_paged(v_cache, block_tables[b], n)
+        out[b] = _sdpa(q[b:b + 1], k, v, scale)[0]
+    return out
+
+
+def prefill_ref(q, k, v, cu_seqlens_q, cu_seqlens_k, scale, block_tables=None):
+    """q [sum Lq,Hq,D] -> fp32 [sum Lq,Hq,D].  ``k``/``v`` are packed rows
+    ``[sum Lk,Hkv,D]`` when block_tables is None, else the cache planes."""
+    out = torch.zeros(q.shape, dtype=torch.float32)
+    B = cu_seqlens_q.numel() - 1
+    for b in range(B):
+        q0, q1 = int(cu_seqlens_q[b]), int(cu_seqlens_q[b + 1])
+        k0, k1 = int(cu_seqlens_k[b]), int(cu_seqlens_k[b + 1])
+        lq, lk = q1 - q0, k1 - k0
+        if lq == 0:
+            continue
+        if block_tables is None:
+            kb, vb = k[k0:k1], v[k0:k1]
+        else:
+            kb, vb = gather_paged(k, block_tables[b], lk), gather_paged(v, block_tables[b], lk)
+        i = torch.arange(lq).unsqueeze(1)
+        j = torch.arange(lk).unsqueeze(0)
+        mask = j <= i + (lk - lq)
+        o = _sdpa(q[q0:q1], kb, vb, scale, mask)
+        dead = ~mask.any(dim=1)  # rows that see no key: zeros, not NaN
+        if dead.any():
+            o[dead] = 0.0
+        out[q0:q1] = o
+    return out
+
+
+def attention_forward_ref(q, k, v, k_cache, v_cache, ctx, scale):
+    """Whole layer on CPU tensors, same control flow as nanovllm/layers/attention.py:58-79.
+    ``ctx`` carries is_prefill, cu_seqlens_q/k, slot_mapping, context_lens, block_tables.
+    Mutates the caches; returns fp32 ``[N, Hq, D]``."""
+    if k_cache.numel() and v_cache.numel():
+        store_kvcache_ref(k, v, k_cache, v_cache, ctx.slot_mapping)
+    if ctx.is_prefill:
+        if ctx.block_tables is not None:
+            return prefill_ref(q, k_cache, v_cache, ctx.cu_seqlens_q, ctx.cu_seqlens_k, scale, ctx.block_tables)
+        return prefill_ref(q, k, v, ctx.cu_seqlens_q, ctx.cu_seqlens_k, scale)
+    return decode_ref(q, k_cache, v_cache, ctx.context_lens, ctx.block_tables, scale)

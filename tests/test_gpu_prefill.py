@@ -1,0 +1,75 @@
+"""Varlen causal GQA prefill on the GPU, through the C ABI, against the fp32 CPU oracle."""
+import pytest
+import torch
+
+from conftest import assert_close_to_oracle
+from nano_vllm_b200 import _lib, attention as A, workloads as W
+from oracle import paged_attention_ref as R
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(cuda, case, what):
+    dev = case.to(cuda)
+    if case.k_cache.numel():
+        A.store_kvcache(dev.k, dev.v, dev.k_cache, dev.v_cache, dev.slot_mapping)
+        R.store_kvcache_ref(case.k, case.v, case.k_cache, case.v_cache, case.slot_mapping)
+    if case.block_tables is not None:
+        out = A.prefill_varlen(dev.q, dev.k_cache, dev.v_cache, dev.cu_seqlens_q, dev.cu_seqlens_k,
+                               case.max_seqlen_q, case.max_seqlen_k, case.scale, block_tables=dev.block_tables)
+        ref = R.prefill_ref(case.q, case.k_cache, case.v_cache, case.cu_seqlens_q, case.cu_seqlens_k, case.scale,
+                            case.block_tables)
+    else:
+        out = A.prefill_varlen(dev.q, dev.k, dev.v, dev.cu_seqlens_q, dev.cu_seqlens_k,
+                               case.max_seqlen_q, case.max_seqlen_k, case.scale)
+        ref = R.prefill_ref(case.q, case.k, case.v, case.cu_seqlens_q, case.cu_seqlens_k, case.scale)
+    torch.cuda.synchronize()
+    assert_close_to_oracle(out, ref, what)
+    if case.k_cache.numel():
+        assert torch.equal(dev.k_cache.cpu().view(torch.int16), case.k_cache.view(torch.int16))
+        assert torch.equal(dev.v_cache.cpu().view(torch.int16), case.v_cache.view(torch.int16))
+    assert _lib.read_status() == 0
+
+
+def test_cfg2(cuda):
+    """BASELINE config 2: 64 prompts in [100,1024], every 4th shares 1-3 cached blocks."""
+    case = W.cfg2_prefill()
+    assert case.block_tables is not None and int(case.cu_seqlens_k[-1]) > int(case.cu_seqlens_q[-1])
+    _check(cuda, case, "cfg2")
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(16, 8, 128), (32, 8, 128), (14, 2, 64), (4, 1, 128), (2, 2, 64)])
+def test_packed_lengths(cuda, hq, hkv, d):
+    case = W.make_prefill_case(21, 8, 1, 1, hq, hkv, d, share_every=0,
+                               lengths=[1, 100, 127, 128, 129, 256, 257, 1024])
+    assert case.block_tables is None
+    _check(cuda, case, f"packed hq{hq} hkv{hkv} d{d}")
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_prefix_cached_blocks(cuda, d):
+    """Lk - Lq in {0, 256, 768}; a fully cached prompt leaves Lq == 0."""
+    case = W.make_prefill_case(22, 6, 1, 1, 8, 2, d, lengths=[1024, 1024, 300, 257, 512, 512],
+                               shared_blocks=[0, 3, 0, 1, 0, 2])
+    lq = (case.cu_seqlens_q[1:] - case.cu_seqlens_q[:-1]).tolist()
+    assert lq == [1024, 256, 300, 1, 512, 0]
+    _check(cuda, case, f"prefix d{d}")
+
+
+def test_warmup_shape_without_cache(cuda):
+    """Engine warm-up: 4096-token sequences before the cache exists
+    (nanovllm/engine/model_runner.py:96-108)."""
+    case = W.make_prefill_case(23, 2, 1, 1, 16, 8, 128, lengths=[4096, 4096], with_cache=False)
+    _check(cuda, case, "warmup")
+
+
+def test_strided_v_view(cuda):
+    hq, hkv, d, n = 16, 8, 128, 700
+    g = torch.Generator().manual_seed(24)
+    qkv = torch.randn(n, (hq + 2 * hkv) * d, generator=g).bfloat16()
+    cu = torch.tensor([0, 300, 700], dtype=torch.int32)
+    q, k, v = (t.view(n, -1, d) for t in qkv.split([hq * d, hkv * d, hkv * d], dim=-1))
+    qd, kd, vd = (t.view(n, -1, d) for t in qkv.to(cuda).split([hq * d, hkv * d, hkv * d], dim=-1))
+    out = A.prefill_varlen(qd, kd, vd, cu.to(cuda), cu.to(cuda), 400, 400, d ** -0.5)
+    ref = R.prefill_ref(q, k, v, cu, cu, d ** -0.5)
+    assert_close_to_oracle(out, ref, "strided")
