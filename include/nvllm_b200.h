@@ -105,6 +105,42 @@ NVLLM_API int nvllm_decode_plan(int32_t batch, int32_t max_blocks, int32_t num_q
                       int32_t num_kv_heads, int32_t head_dim,
                       int32_t* chunk_tokens, int32_t* max_splits);
 
+/* Size of the scratch array built into the library for nvllm_decode_paged_static. */
+#define NVLLM_DECODE_STATIC_SCRATCH_BYTES (32ll << 20)
+
+/*
+ * nvllm_decode_paged for callers that cannot supply a workspace.  No counterpart in the
+ * reference (flash-attn allocates its split-KV scratch through torch on every call).
+ *
+ * Who needs it: a host that must not, or cannot, allocate device memory once it is serving —
+ * an engine that has handed every free byte of HBM to its KV cache, a latency-critical loop
+ * that cannot afford the device-wide synchronisation an allocation may imply, or a thin
+ * binding that only forwards pointers it received and owns no allocator.  Inputs and the
+ * output are still the caller's buffers; only the split-KV partials move into the library.
+ *
+ * Same arguments and results as nvllm_decode_paged minus the workspace pair.  The partials go
+ * to a 32 MiB (NVLLM_DECODE_STATIC_SCRATCH_BYTES) array that is part of the library image, so
+ * every GPU whose context loads the library carries those 32 MiB until the process exits.
+ * The call never allocates or frees anything.  Limits and rules:
+ *   - a geometry whose nvllm_decode_workspace_bytes() exceeds the array is refused with
+ *     NVLLM_E_WORKSPACE before anything is launched (e.g. batch 512 with 32 query heads and
+ *     4 splits); use the workspace variant for those;
+ *   - the first call on each device looks up the array's device address (with that device
+ *     current); make that first call outside stream capture;
+ *   - all calls on a device share the one array, which still holds whatever the previous
+ *     call left there.  The kernels never read a value they did not write in the same call,
+ *     so nothing needs clearing; but two calls whose kernels may run at the same time on one
+ *     GPU (different streams, or graphs replayed concurrently) would overwrite each other's
+ *     partials — keep calls to this entry point ordered on a device.
+ */
+NVLLM_API int nvllm_decode_paged_static(const void* q, int64_t q_row_stride,
+                              const void* k_cache, const void* v_cache,
+                              const int32_t* context_lens,
+                              const int32_t* block_tables, int64_t bt_row_stride, int32_t max_blocks,
+                              void* out, int64_t out_row_stride,
+                              int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                              float scale, int64_t num_blocks, void* stream);
+
 /*
  * Varlen causal GQA prefill.  Replaces the flash_attn_varlen_func call
  * (nanovllm/layers/attention.py:67-73).  For sequence b, query row i (0-based among its

@@ -18,6 +18,9 @@ SIGNATURES = {
     "nvllm_decode_paged": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32,
                                      c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_float, c_int64,
                                      c_void_p, c_int64, c_void_p]),
+    "nvllm_decode_paged_static": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32,
+                                            c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_float, c_int64,
+                                            c_void_p]),
     "nvllm_decode_workspace_bytes": (c_int64, [c_int32, c_int32, c_int32, c_int32, c_int32]),
     "nvllm_decode_plan": (c_int32, [c_int32, c_int32, c_int32, c_int32, c_int32, POINTER(c_int32), POINTER(c_int32)]),
     "nvllm_prefill_varlen": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,

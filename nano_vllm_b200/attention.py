@@ -125,6 +125,35 @@ def decode_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     return out
 
 
+def decode_paged_static(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, context_lens: torch.Tensor,
+                        block_tables: torch.Tensor, scale: float, out: torch.Tensor) -> torch.Tensor:
+    """``decode_paged`` for hosts that may not allocate device memory while serving (all free
+    HBM already belongs to the KV cache, or an allocation's implicit synchronisation is not
+    acceptable): the split-KV partials go to a 32 MiB array inside the library instead of a
+    torch-allocated workspace, and ``out`` must be supplied, so this call allocates nothing.
+    Raises ``NvllmError`` (NVLLM_E_WORKSPACE) for geometries whose scratch exceeds the array.
+    Calls on one device share that array: keep them ordered on the GPU.  Make the first call
+    on a device outside CUDA graph capture.  No counterpart in nano-vllm."""
+    B, Hq, D = q.shape
+    Hkv = k_cache.shape[-2]
+    _require_cuda_bf16("q", q)
+    _require_cuda_bf16("k_cache", k_cache)
+    _require_cuda_bf16("v_cache", v_cache)
+    _require_cuda_bf16("out", out)
+    _require_i32("context_lens", context_lens)
+    _require_i32("block_tables", block_tables)
+    assert q.stride(-1) == 1 and q.stride(1) == D and out.stride(-1) == 1 and out.stride(1) == D
+    assert k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert block_tables.dim() == 2 and block_tables.shape[0] == B and context_lens.numel() == B
+    num_blocks = k_cache.numel() // (BLOCK_SIZE * Hkv * D)
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.load().nvllm_decode_paged_static(
+            q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
+            context_lens.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), block_tables.shape[1],
+            out.data_ptr(), out.stride(0), B, Hq, Hkv, D, float(scale), num_blocks, _stream(q)))
+    return out
+
+
 def prefill_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens_q: torch.Tensor,
                    cu_seqlens_k: torch.Tensor, max_seqlen_q: int, max_seqlen_k: int, scale: float,
                    block_tables: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:

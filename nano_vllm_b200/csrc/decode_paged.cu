@@ -459,3 +459,71 @@ extern "C" int nvllm_decode_paged(const void* q, int64_t q_row_stride, const voi
   if (head_dim == 128) return launch_decode<DecodeCfg<128, 16, 3, 4>>(p, st);
   return launch_decode<DecodeCfg<64, 32, 3, 4>>(p, st);
 }
+
+// ---- decode without a caller-provided workspace ---------------------------------------------
+//
+// nvllm_decode_paged_static is for hosts that have no way to hand the library a scratch
+// buffer: an engine that has already given all free HBM to its KV cache (nano-vllm sizes the
+// cache from whatever memory is left, so a later allocation can fail), a real-time serving
+// loop in which cudaMalloc's implicit device synchronisation is unacceptable, or a binding
+// from a language that owns no device allocator and only forwards the pointers it was given.
+// The split-KV partials live in a fixed array that is part of the library image.
+
+namespace nvllm {
+
+constexpr int64_t kStaticScratchBytes = NVLLM_DECODE_STATIC_SCRATCH_BYTES;
+
+// Lives in every context that loads this library, for the life of the process.  In host
+// code this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char g_decode_static_scratch[kStaticScratchBytes];
+
+// Device address of the array on each device, resolved on that device's first call.
+static void* g_static_scratch_addr[64] = {nullptr};
+
+static int static_scratch(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    (void)cudaGetLastError();
+    return fail(NVLLM_E_NO_DEVICE, "decode_paged_static: no usable CUDA device is current");
+  }
+  if (!g_static_scratch_addr[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_decode_static_scratch);
+    if (e != cudaSuccess || !p) {
+      (void)cudaGetLastError();
+      return fail(NVLLM_E_CUDA, "decode_paged_static: cudaGetSymbolAddress failed on device %d: %s", dev,
+                  cudaGetErrorString(e));
+    }
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return NVLLM_OK;
+}
+
+}  // namespace nvllm
+
+extern "C" int nvllm_decode_paged_static(const void* q, int64_t q_row_stride, const void* k_cache,
+                                         const void* v_cache, const int32_t* context_lens,
+                                         const int32_t* block_tables, int64_t bt_row_stride, int32_t max_blocks,
+                                         void* out, int64_t out_row_stride, int32_t batch, int32_t num_q_heads,
+                                         int32_t num_kv_heads, int32_t head_dim, float scale, int64_t num_blocks,
+                                         void* stream) {
+  using namespace nvllm;
+  const int64_t need = nvllm_decode_workspace_bytes(batch, max_blocks, num_q_heads, num_kv_heads, head_dim);
+  if (need < 0) return static_cast<int>(need);  // geometry rejected; message already set
+  if (need > kStaticScratchBytes)
+    return fail(NVLLM_E_WORKSPACE,
+                "decode_paged_static: this geometry needs %lld bytes of split-KV scratch but the built-in array "
+                "holds %lld; use nvllm_decode_paged with a caller-owned workspace",
+                (long long)need, (long long)kStaticScratchBytes);
+  void* scratch = nullptr;
+  int rc = static_scratch(&scratch);
+  if (rc) return rc;
+  // Nothing in the scratch has to start at zero: every partial that the combine kernel reads
+  // is written by the partial kernel of the same call, so leftovers from earlier calls are
+  // never observed.
+  return nvllm_decode_paged(q, q_row_stride, k_cache, v_cache, context_lens, block_tables, bt_row_stride, max_blocks,
+                            out, out_row_stride, batch, num_q_heads, num_kv_heads, head_dim, scale, num_blocks,
+                            scratch, kStaticScratchBytes, stream);
+}
