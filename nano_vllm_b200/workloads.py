@@ -139,6 +139,8 @@ def make_prefill_case(seed: int, batch: int, len_lo: int, len_hi: int, hq: int, 
                     shared[i] = max(s, 0)
     else:
         shared = list(shared_blocks)
+        for i, s_ in enumerate(shared):  # only whole blocks of the predecessor can be shared
+            assert s_ == 0 or (i > 0 and s_ <= lens[i - 1] // BLOCK_SIZE and s_ * BLOCK_SIZE <= lens[i])
     cached = [s * BLOCK_SIZE for s in shared]
     lq = [lens[i] - cached[i] for i in range(batch)]
     assert all(x >= 0 for x in lq)

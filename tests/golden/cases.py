@@ -1,0 +1,62 @@
+"""Seeded cases shared by the golden-vector recorder (make_golden.py, runs the reference on a
+GPU) and the tests that replay them (CPU oracle and CUDA kernels)."""
+from __future__ import annotations
+
+import hashlib
+import sys
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parents[2]
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+from nano_vllm_b200 import workloads as W  # noqa: E402
+
+GOLDEN_DIR = Path(__file__).resolve().parent
+
+
+def decode_cases():
+    return {
+        "decode_qwen3_g2_d128": W.make_decode_case(101, 6, 1, 1, 16, 8, 128, context_lens=[1, 255, 256, 257, 1024, 700]),
+        "decode_qwen3_8b_g4_d128": W.make_decode_case(102, 4, 1, 1, 8, 2, 128, context_lens=[100, 513, 2048, 1]),
+        "decode_qwen2_g7_d64": W.make_decode_case(103, 5, 1, 1, 14, 2, 64, context_lens=[1, 255, 256, 257, 1024]),
+    }
+
+
+def prefill_cases():
+    return {
+        "prefill_packed_d128": W.make_prefill_case(201, 5, 1, 1, 4, 2, 128, share_every=0, lengths=[1, 100, 256, 257, 300]),
+        "prefill_prefix_d128": W.make_prefill_case(202, 4, 1, 1, 4, 2, 128, lengths=[600, 600, 800, 1024],
+                                                   shared_blocks=[0, 2, 0, 3]),
+        "prefill_prefix_d64_g7": W.make_prefill_case(203, 3, 1, 1, 14, 2, 64, lengths=[300, 520, 257],
+                                                     shared_blocks=[0, 1, 1]),
+    }
+
+
+def store_cases():
+    """(key, value, k_cache, v_cache, slot_mapping) with permuted slots and a strided value."""
+    out = {}
+    for name, (seed, n, hkv, d) in {"store_qwen3": (301, 300, 8, 128), "store_qwen2": (302, 77, 2, 64)}.items():
+        g = torch.Generator().manual_seed(seed)
+        kv = torch.randn(n, 2 * hkv * d, generator=g).bfloat16()
+        key, value = (t.view(n, hkv, d) for t in kv.split(hkv * d, dim=-1))  # both strided views
+        k_cache = torch.randn(3, 256, hkv, d, generator=g).bfloat16()
+        v_cache = torch.randn(3, 256, hkv, d, generator=g).bfloat16()
+        slots = torch.randperm(3 * 256, generator=g)[:n].to(torch.int32)
+        out[name] = (key, value, k_cache, v_cache, slots)
+    return out
+
+
+def sha(t: torch.Tensor) -> str:
+    return hashlib.sha256(t.contiguous().view(torch.uint8).numpy().tobytes()).hexdigest()
+
+
+def input_fingerprint(*tensors) -> str:
+    """Detects a change in the seeded generators between recording and replay."""
+    h = hashlib.sha256()
+    for t in tensors:
+        if t is not None:
+            h.update(t.contiguous().view(torch.uint8).numpy().tobytes())
+    return h.hexdigest()

@@ -1,0 +1,78 @@
+"""The C-ABI library: loads without a GPU, exports every declared symbol, and rejects bad
+arguments on the host before touching a device."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from nano_vllm_b200 import _lib
+
+HEADER = Path(__file__).resolve().parents[1] / "include" / "nvllm_b200.h"
+
+
+def declared_symbols():
+    text = HEADER.read_text()
+    return re.findall(r"NVLLM_API\s+[\w\s\*]+?\b(nvllm_\w+)\s*\(", text)
+
+
+def test_every_declared_symbol_is_exported_and_bound(lib):
+    names = declared_symbols()
+    assert len(names) >= 10
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in the header but not exported"
+    assert sorted(names) == sorted(_lib.SIGNATURES), "ctypes table and header disagree"
+    assert lib.nvllm_abi_version() == 1
+
+
+def test_decode_plan_is_pure_host_arithmetic(lib):
+    # large batch: few splits; small batch: many splits, never smaller than a block
+    chunk, splits = _lib.decode_plan(256, 16, 16, 8, 128)
+    assert chunk % 256 == 0 and splits == -(-16 * 256 // chunk)
+    chunk1, splits1 = _lib.decode_plan(1, 16, 16, 8, 128)
+    assert chunk1 == 256 and splits1 == 16
+    chunk5, splits5 = _lib.decode_plan(512, 128, 14, 2, 64)
+    assert chunk5 <= 4096 and chunk5 * splits5 >= 128 * 256
+    # the plan depends on static sizes only: same inputs, same plan
+    assert _lib.decode_plan(256, 16, 16, 8, 128) == (chunk, splits)
+    ws = _lib.decode_workspace_bytes(256, 16, 16, 8, 128)
+    assert ws == (0 if splits == 1 else 256 * 16 * splits * (128 + 2) * 4)
+
+
+@pytest.mark.parametrize("hq,hkv,d,code", [(16, 8, 96, -3), (16, 3, 128, -3), (32, 2, 128, -3), (0, 0, 128, -3)])
+def test_unsupported_geometry_is_rejected(lib, hq, hkv, d, code):
+    assert lib.nvllm_decode_workspace_bytes(4, 4, hq, hkv, d) == code
+    assert _lib.last_error() != ""
+    with pytest.raises(_lib.NvllmError):
+        _lib.decode_plan(4, 4, hq, hkv, d)
+
+
+def test_null_and_misaligned_arguments_are_rejected_before_any_launch(lib):
+    p16, p8 = ctypes.c_void_p(4096), ctypes.c_void_p(4096 + 8)
+    # store: NULL, bad row size, misaligned pointer, stride shorter than the row
+    assert lib.nvllm_store_kvcache(None, 1024, p16, 1024, p16, p16, p16, 4, 1024, 256, None) == -1
+    assert lib.nvllm_store_kvcache(p16, 1024, p16, 1024, p16, p16, p16, 4, 1020, 256, None) == -3
+    assert lib.nvllm_store_kvcache(p8, 1024, p16, 1024, p16, p16, p16, 4, 1024, 256, None) == -2
+    assert lib.nvllm_store_kvcache(p16, 512, p16, 1024, p16, p16, p16, 4, 1024, 256, None) == -3
+    assert lib.nvllm_store_kvcache(p16, 1028, p16, 1024, p16, p16, p16, 4, 1024, 256, None) == -2
+    assert lib.nvllm_store_kvcache(p16, 1024, p16, 1024, p16, p16, p16, 0, 1024, 256, None) == 0  # nothing to do
+    # decode: missing workspace when the plan splits
+    assert _lib.decode_plan(2, 16, 16, 8, 128)[1] > 1
+    rc = lib.nvllm_decode_paged(p16, 2048, p16, p16, p16, p16, 16, 16, p16, 2048, 2, 16, 8, 128,
+                                ctypes.c_float(0.1), 100, None, 0, None)
+    assert rc == -4 and "workspace" in _lib.last_error()
+    rc = lib.nvllm_decode_paged(p8, 2048, p16, p16, p16, p16, 16, 16, p16, 2048, 2, 16, 8, 128,
+                                ctypes.c_float(0.1), 100, p16, 1 << 30, None)
+    assert rc == -2
+    # prefill: NULL cu_seqlens, short stride, paged mode without a table width
+    rc = lib.nvllm_prefill_varlen(p16, 2048, p16, 1024, p16, 1024, None, 0, 0, p16, 2048, None, p16, 2, 100, 100,
+                                  16, 8, 128, ctypes.c_float(0.1), 0, None)
+    assert rc == -1
+    rc = lib.nvllm_prefill_varlen(p16, 2048, p16, 512, p16, 1024, None, 0, 0, p16, 2048, p16, p16, 2, 100, 100,
+                                  16, 8, 128, ctypes.c_float(0.1), 0, None)
+    assert rc == -3
+    rc = lib.nvllm_prefill_varlen(p16, 2048, p16, 1024, p16, 1024, p16, 4, 0, p16, 2048, p16, p16, 2, 100, 100,
+                                  16, 8, 128, ctypes.c_float(0.1), 10, None)
+    assert rc == -3
+    assert lib.nvllm_prefill_varlen(p16, 2048, p16, 1024, p16, 1024, None, 0, 0, p16, 2048, p16, p16, 0, 0, 0,
+                                    16, 8, 128, ctypes.c_float(0.1), 0, None) == 0  # empty batch

@@ -1,0 +1,61 @@
+"""Pins the CPU oracle to outputs recorded from the reference implementation itself
+(tests/golden/README.md).  Runs without a GPU."""
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parent / "golden"))
+import cases as C  # noqa: E402
+
+from conftest import assert_close_to_oracle
+from oracle import paged_attention_ref as R
+
+
+def _load(name):
+    z = np.load(C.GOLDEN_DIR / f"{name}.npz")
+    return {k: z[k] for k in z.files}
+
+
+def _bf16(a):
+    return torch.from_numpy(a.copy()).view(torch.bfloat16)
+
+
+@pytest.mark.parametrize("name", sorted(C.store_cases()))
+def test_store_digest_matches_reference(name):
+    key, value, k_cache, v_cache, slots = C.store_cases()[name]
+    gold = _load(name)
+    assert str(gold["inputs"]) == C.input_fingerprint(key, value, k_cache, v_cache, slots), "seeded inputs drifted"
+    R.store_kvcache_ref(key, value, k_cache, v_cache, slots)
+    assert C.sha(k_cache) == str(gold["k_cache_sha"])
+    assert C.sha(v_cache) == str(gold["v_cache_sha"])
+
+
+@pytest.mark.parametrize("name", sorted(C.decode_cases()))
+def test_decode_oracle_matches_reference(name):
+    case = C.decode_cases()[name]
+    gold = _load(name)
+    assert str(gold["inputs"]) == C.input_fingerprint(case.q, case.k_new, case.v_new, case.k_cache, case.v_cache,
+                                                      case.context_lens, case.block_tables, case.slot_mapping)
+    R.store_kvcache_ref(case.k_new, case.v_new, case.k_cache, case.v_cache, case.slot_mapping)
+    assert C.sha(case.k_cache) == str(gold["k_cache_sha"]) and C.sha(case.v_cache) == str(gold["v_cache_sha"])
+    ref = R.decode_ref(case.q, case.k_cache, case.v_cache, case.context_lens, case.block_tables, case.scale)
+    assert_close_to_oracle(_bf16(gold["out"]), ref, name)
+
+
+@pytest.mark.parametrize("name", sorted(C.prefill_cases()))
+def test_prefill_oracle_matches_reference(name):
+    case = C.prefill_cases()[name]
+    gold = _load(name)
+    assert str(gold["inputs"]) == C.input_fingerprint(case.q, case.k, case.v, case.cu_seqlens_q, case.cu_seqlens_k,
+                                                      case.slot_mapping, case.block_tables)
+    R.store_kvcache_ref(case.k, case.v, case.k_cache, case.v_cache, case.slot_mapping)
+    assert C.sha(case.k_cache) == str(gold["k_cache_sha"]) and C.sha(case.v_cache) == str(gold["v_cache_sha"])
+    if case.block_tables is not None:
+        ref = R.prefill_ref(case.q, case.k_cache, case.v_cache, case.cu_seqlens_q, case.cu_seqlens_k, case.scale,
+                            case.block_tables)
+    else:
+        ref = R.prefill_ref(case.q, case.k, case.v, case.cu_seqlens_q, case.cu_seqlens_k, case.scale)
+    assert_close_to_oracle(_bf16(gold["out"]), ref, name)
