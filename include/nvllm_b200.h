@@ -56,6 +56,7 @@ extern "C" {
 /* bits of the device status word */
 #define NVLLM_STATUS_BAD_SLOT 1  /* store_kvcache saw slot >= num_slots (row skipped) */
 #define NVLLM_STATUS_BAD_BLOCK 2 /* a block_tables entry in use was outside [0,num_blocks) */
+#define NVLLM_STATUS_TIMEOUT 4   /* a bounded in-kernel wait expired; that launch's output is invalid */
 
 /*
  * Scatter the new tokens' K and V rows into the paged cache.
@@ -152,7 +153,10 @@ NVLLM_API int nvllm_decode_paged_static(const void* q, int64_t q_row_stride,
  *   - paged (block_tables != NULL): k / v are the cache planes and key j of sequence b is
  *     slot block_tables[b, j/256]*256 + j%256; the k/v row strides are ignored.
  * q/out: [total_q, Hq, D] with the given row strides.  Lq_b == 0 is legal (no work).
- * Supported: D in {64,128}; Hq % Hkv == 0.
+ * total_q / total_k are the row counts of q and of packed k/v (ignored for k/v in paged
+ * mode); they bound the tiled loads, nothing past them is read.
+ * Supported: D in {64,128}; Hq % Hkv == 0.  D == 128 runs on the tcgen05 kernel, which
+ * needs every K/V row the table or cu_seqlens_k makes visible to hold finite values.
  */
 NVLLM_API int nvllm_prefill_varlen(const void* q, int64_t q_row_stride,
                          const void* k, int64_t k_row_stride,
@@ -160,9 +164,16 @@ NVLLM_API int nvllm_prefill_varlen(const void* q, int64_t q_row_stride,
                          const int32_t* block_tables, int64_t bt_row_stride, int32_t max_blocks,
                          void* out, int64_t out_row_stride,
                          const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                         int64_t total_q, int64_t total_k,
                          int32_t batch, int32_t max_seqlen_q, int32_t max_seqlen_k,
                          int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
                          float scale, int64_t num_blocks, void* stream);
+
+/* Known-answer check of the tensor-core building blocks the prefill kernel is made of
+ * (TMA swizzled loads, shared-memory and instruction descriptors, TMEM loads and stores):
+ * out_ss = A B^T and out_ts = A B for A, B [128,128] bf16 row-major, outputs [128,128] fp32.
+ * A diagnostic for new driver / toolkit versions.  No counterpart in the reference. */
+NVLLM_API int nvllm_selftest_umma(const void* a, const void* b, float* out_ss, float* out_ts, void* stream);
 
 /* Message for the last negative return value on this thread ("" if none).
  * No counterpart in the reference (it raises Python exceptions). */

@@ -192,7 +192,8 @@ def prefill_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens
         _lib.check(_lib.load().nvllm_prefill_varlen(
             q.data_ptr(), q.stride(0), k.data_ptr(), k_stride, v.data_ptr(), v_stride,
             bt_ptr, bt_stride, max_blocks, out.data_ptr(), out.stride(0),
-            cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), batch, int(max_seqlen_q), int(max_seqlen_k),
+            cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), N, 0 if block_tables is not None else k.shape[0],
+            batch, int(max_seqlen_q), int(max_seqlen_k),
             Hq, Hkv, D, float(scale), num_blocks, _stream(q)))
     return out
 

@@ -7,8 +7,8 @@
 extern "C" int nvllm_prefill_varlen(const void* q, int64_t q_row_stride, const void* k, int64_t k_row_stride,
                                     const void* v, int64_t v_row_stride, const int32_t* block_tables,
                                     int64_t bt_row_stride, int32_t max_blocks, void* out, int64_t out_row_stride,
-                                    const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int32_t batch,
-                                    int32_t max_seqlen_q, int32_t max_seqlen_k, int32_t num_q_heads,
+                                    const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int64_t total_q,
+                                    int64_t total_k, int32_t batch, int32_t max_seqlen_q, int32_t max_seqlen_k, int32_t num_q_heads,
                                     int32_t num_kv_heads, int32_t head_dim, float scale, int64_t num_blocks,
                                     void* stream) {
   using namespace nvllm;
@@ -20,7 +20,8 @@ extern "C" int nvllm_prefill_varlen(const void* q, int64_t q_row_stride, const v
     return fail(NVLLM_E_GEOMETRY, "prefill_varlen: batch=%d / Hq=%d outside the launch limits", batch, num_q_heads);
   if (max_seqlen_q < 0 || max_seqlen_k < 0)
     return fail(NVLLM_E_GEOMETRY, "prefill_varlen: negative max_seqlen");
-  if (batch == 0 || max_seqlen_q == 0) return NVLLM_OK;
+  if (total_q < 0 || total_k < 0) return fail(NVLLM_E_GEOMETRY, "prefill_varlen: negative total_q / total_k");
+  if (batch == 0 || max_seqlen_q == 0 || total_q == 0) return NVLLM_OK;
   if (!q || !k || !v || !out || !cu_seqlens_q || !cu_seqlens_k)
     return fail(NVLLM_E_NULL, "prefill_varlen: NULL pointer argument");
   const int64_t qrow = static_cast<int64_t>(num_q_heads) * head_dim;
@@ -63,5 +64,11 @@ extern "C" int nvllm_prefill_varlen(const void* q, int64_t q_row_stride, const v
   p.d = head_dim;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.num_blocks = num_blocks;
+  static const bool force_mma = [] {
+    const char* s = std::getenv("NVLLM_PREFILL_IMPL");
+    return s && s[0] == 'm';
+  }();
+  if (head_dim == 128 && !force_mma && (block_tables || total_k > 0))
+    return launch_prefill_tc(p, total_q, total_k, static_cast<cudaStream_t>(stream));
   return launch_prefill_mma(p, static_cast<cudaStream_t>(stream));
 }

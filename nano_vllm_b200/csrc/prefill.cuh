@@ -27,5 +27,7 @@ struct PrefillParams {
 
 // Warp-level mma.sync kernel: every supported geometry.
 int launch_prefill_mma(const PrefillParams& p, cudaStream_t stream);
+// tcgen05 / TMEM / TMA kernel: head_dim 128.  total_q / total_k bound the tiled loads.
+int launch_prefill_tc(const PrefillParams& p, int64_t total_q, int64_t total_k, cudaStream_t stream);
 
 }  // namespace nvllm

@@ -1,0 +1,418 @@
+// Varlen causal GQA prefill on the 5th-generation tensor cores (tcgen05 + TMEM + TMA),
+// head_dim 128.
+//
+// Math follows the prefill branch of nanovllm/layers/attention.py:67-73
+// (flash_attn_varlen_func, causal, optional block table).
+//
+// One thread block = one 128-row query tile of one (sequence, query head); two blocks are
+// resident per SM (96 KB of shared memory and 256 of the 512 TMEM columns each), so one
+// block's softmax overlaps the other's matrix products.  Six warps with fixed roles:
+//   warps 0-3  softmax / correction / epilogue: thread r owns query row r.  It reads its row
+//              of S from TMEM (tcgen05.ld, lane = row, so max and sum need no shuffles),
+//              writes P as packed bf16 back into the same TMEM columns (tcgen05.st) and,
+//              when the running maximum has grown by more than 2^8, rescales its row of O.
+//   warp 4     TMA producer (one lane): Q once, then one K tile and one V tile per step,
+//              each as two 128-row x 64-column boxes with the 128-byte swizzle.
+//   warp 5     MMA issuer (one lane): S = Q K^T (SS form, both operands K-major in shared
+//              memory), then O += P V (TS form: P from TMEM, V as an MN-major shared-memory
+//              operand); completion is signalled to mbarriers with tcgen05.commit.
+// K and V are single-buffered: the K buffer is released when S is complete, the V buffer
+// when O += P V is complete, so the next loads run under the softmax of the current tile.
+// Every mbarrier wait is bounded; on expiry the block records NVLLM_STATUS_TIMEOUT, all roles
+// leave their loops and TMEM is freed.
+#include "common.cuh"
+#include "prefill.cuh"
+#include "sm100.cuh"
+
+namespace nvllm {
+using namespace sm100;
+
+namespace tc {
+constexpr int BM = 128, BN = 128, D = 128;
+constexpr int TILE_BYTES = BM * D * 2;   // 32 KB: two [128 x 64] swizzled sub-tiles
+constexpr int SUB_BYTES = TILE_BYTES / 2;
+constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = 2 * TILE_BYTES, OFF_BAR = 3 * TILE_BYTES;
+constexpr int SMEM = 3 * TILE_BYTES + 256 + 1024;  // + barriers + alignment slack
+constexpr int TMEM_COLS = 256;                      // S/P: columns [0,128), O: [128,256)
+constexpr int NTHREADS = 192;
+constexpr float kRescaleThreshold = 8.f;            // log2 units
+enum Bar { Q_FULL = 0, K_FULL, V_FULL, K_EMPTY, V_EMPTY, S_FULL, P_FULL, O_FULL, DRAIN, NUM_BARS };
+}  // namespace tc
+
+// Bounded wait that also gives up as soon as another role has aborted.
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 128; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(tc::NTHREADS, 2)
+prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tmap_q,
+                  const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v) {
+  using namespace tc;
+  extern __shared__ unsigned char smem_raw[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  const int b = blockIdx.z, h = blockIdx.y, kvh = h / p.g;
+  const int mtile = gridDim.x - 1 - blockIdx.x;  // long tiles first
+  const int q0 = p.cu_q[b], Lq = p.cu_q[b + 1] - q0;
+  const int k0 = p.cu_k[b], Lk = p.cu_k[b + 1] - k0;
+  const int m0 = mtile * BM;
+  if (m0 >= Lq) return;
+  const int off = Lk - Lq;
+  int kv_end = min(Lk, min(m0 + BM, Lq) + off);
+  if (kv_end < 0) kv_end = 0;
+  const int n_kv = (kv_end + BN - 1) / BN;
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + OFF_BAR;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + OFF_BAR + 8 * NUM_BARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + OFF_BAR + 8 * NUM_BARS + 8);
+
+  if (tid == 0) {
+    for (int i = 0; i < NUM_BARS; ++i) mbar_init(bar(i), i == P_FULL ? 128u : 1u);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 5) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_s = tmem, tmem_o = tmem + 128;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_kv > 0) {
+      prefetch_tmap(&tmap_q);
+      prefetch_tmap(&tmap_k);
+      prefetch_tmap(&tmap_v);
+      mbar_expect_tx(bar(Q_FULL), TILE_BYTES);
+      tma_load_3d(base + OFF_Q, &tmap_q, bar(Q_FULL), 0, h, q0 + m0);
+      tma_load_3d(base + OFF_Q + SUB_BYTES, &tmap_q, bar(Q_FULL), 64, h, q0 + m0);
+      const int32_t* bt_row = p.block_tables ? p.block_tables + b * p.bt_stride : nullptr;
+      for (int j = 0; j < n_kv; ++j) {
+        int row;
+        if (bt_row) {
+          int64_t blk = bt_row[(j * BN) / kBlockSize];
+          if (blk < 0 || blk >= p.num_blocks) {
+            atomicOr(p.status, NVLLM_STATUS_BAD_BLOCK);
+            blk = 0;
+          }
+          row = static_cast<int>(blk * kBlockSize + (j * BN) % kBlockSize);
+        } else {
+          row = k0 + j * BN;
+        }
+        if (j > 0 && !wait_or_abort(bar(K_EMPTY), (j - 1) & 1, abort_flag)) break;
+        mbar_expect_tx(bar(K_FULL), TILE_BYTES);
+        tma_load_3d(base + OFF_K, &tmap_k, bar(K_FULL), 0, kvh, row);
+        tma_load_3d(base + OFF_K + SUB_BYTES, &tmap_k, bar(K_FULL), 64, kvh, row);
+        if (j > 0 && !wait_or_abort(bar(V_EMPTY), (j - 1) & 1, abort_flag)) break;
+        mbar_expect_tx(bar(V_FULL), TILE_BYTES);
+        tma_load_3d(base + OFF_V, &tmap_v, bar(V_FULL), 0, kvh, row);
+        tma_load_3d(base + OFF_V + SUB_BYTES, &tmap_v, bar(V_FULL), 64, kvh, row);
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_kv > 0) {
+      constexpr uint32_t idesc_qk = umma_idesc(BM, BN, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc(BM, D, 0, 1);
+      bool ok = wait_or_abort(bar(Q_FULL), 0, abort_flag);
+      for (int j = 0; ok && j < n_kv; ++j) {
+        if (!(ok = wait_or_abort(bar(K_FULL), j & 1, abort_flag))) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t koff = (ks >> 2) * SUB_BYTES + (ks & 3) * 32;
+          umma_ss(tmem_s, umma_desc(base + OFF_Q + koff, 16, 1024), umma_desc(base + OFF_K + koff, 16, 1024),
+                  idesc_qk, ks > 0);
+        }
+        umma_commit(bar(S_FULL));
+        umma_commit(bar(K_EMPTY));
+        if (!(ok = wait_or_abort(bar(V_FULL), j & 1, abort_flag))) break;
+        if (!(ok = wait_or_abort(bar(P_FULL), j & 1, abort_flag))) break;
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < BN / 16; ++ks) {
+          umma_ts(tmem_o, tmem_s + ks * 8, umma_desc(base + OFF_V + ks * 2048, SUB_BYTES, 1024), idesc_pv,
+                  (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(bar(V_EMPTY));
+        if (j == n_kv - 1) umma_commit(bar(O_FULL));
+      }
+      if (!ok) {  // make sure nothing is still running on TMEM before it is freed
+        umma_commit(bar(DRAIN));
+        (void)mbar_wait(bar(DRAIN), 0);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax rows
+    const int r = warp * 32 + lane;
+    const int qi = m0 + r;  // query index within the sequence
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      if (!(ok = wait_or_abort(bar(S_FULL), j & 1, abort_flag))) break;
+      tc_fence_after();
+      uint32_t s[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s + lane_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+      tmem_wait_ld();
+
+      const int j0 = j * BN;
+      const int limit = min(qi + off, Lk - 1) - j0;  // columns c <= limit are visible
+      const bool need_mask = (j0 + BN - 1 > m0 + off) || (j0 + BN > Lk);
+      float mx = -INFINITY;
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c) {
+          float v = __uint_as_float(s[c]);
+          v = (c <= limit) ? v : -INFINITY;
+          s[c] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(s[c]));
+      }
+      const float m_new = fmaxf(m_used, mx * p.scale_log2e);
+      // lazy rescale: keep the old reference maximum unless it has been outgrown by 2^8
+      const bool grow = m_new > m_used + kRescaleThreshold || (m_used == -INFINITY && m_new > -INFINITY);
+      if (__any_sync(0xffffffffu, grow)) {
+        float alpha = 1.f;
+        if (grow) {
+          alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
+          m_used = m_new;
+          l *= alpha;
+        }
+        if (j > 0) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tmem_o + lane_addr + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st32(tmem_o + lane_addr + c * 32, o);
+          }
+        }
+      }
+      const float msub = (m_used == -INFINITY) ? 0.f : m_used;
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {  // P is packed in place: s[c] <- (p[2c], p[2c+1])
+        const float p0 = fast_exp2(fmaf(__uint_as_float(s[2 * c]), p.scale_log2e, -msub));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(s[2 * c + 1]), p.scale_log2e, -msub));
+        sum += p0 + p1;
+        s[c] = pack_bf16x2(p0, p1);
+      }
+      l += sum;
+      tmem_st32(tmem_s + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_st32(tmem_s + lane_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(P_FULL));
+    }
+    // epilogue: O / l -> bf16 -> global (rows past the sequence end are not written)
+    if (ok && n_kv > 0) ok = wait_or_abort(bar(O_FULL), 0, abort_flag);
+    tc_fence_after();
+    const float inv = (ok && l > 0.f) ? 1.f / l : 0.f;
+    __nv_bfloat16* dst = p.out + static_cast<int64_t>(q0 + qi) * p.out_stride + h * D;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t o[32];
+      if (n_kv > 0 && ok) {
+        tmem_ld32(tmem_o + lane_addr + c * 32, o);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[e] = 0u;
+      }
+      if (qi < Lq) {
+#pragma unroll
+        for (int e = 0; e < 32; e += 8) {
+          uint4 v;
+          v.x = pack_bf16x2(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
+          v.y = pack_bf16x2(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
+          v.z = pack_bf16x2(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
+          v.w = pack_bf16x2(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
+          *reinterpret_cast<uint4*>(dst + c * 32 + e) = v;
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && *abort_flag) atomicOr(p.status, NVLLM_STATUS_TIMEOUT);
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// ---- known-answer check of the building blocks --------------------------------------------
+// out1 = A B^T   (SS form: A and B both K-major tiles in shared memory)
+// out2 = A B     (TS form: A as packed bf16 in TMEM, B as an MN-major shared-memory tile)
+// A, B: [128,128] bf16 row-major; out1, out2: [128,128] fp32.
+__global__ void __launch_bounds__(160, 1)
+umma_selftest_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                     const __nv_bfloat16* __restrict__ a, float* __restrict__ out1, float* __restrict__ out2,
+                     int* __restrict__ status) {
+  using namespace tc;
+  extern __shared__ unsigned char smem_raw[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + 2 * TILE_BYTES;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + 2 * TILE_BYTES + 64);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + 2 * TILE_BYTES + 72);
+  if (tid == 0) {
+    mbar_init(bar(0), 1);    // tiles landed
+    mbar_init(bar(1), 1);    // SS product done
+    mbar_init(bar(2), 128);  // P written
+    mbar_init(bar(3), 1);    // TS product done
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t A = base, B = base + TILE_BYTES;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_expect_tx(bar(0), 2 * TILE_BYTES);
+      tma_load_3d(A, &tmap_a, bar(0), 0, 0, 0);
+      tma_load_3d(A + SUB_BYTES, &tmap_a, bar(0), 64, 0, 0);
+      tma_load_3d(B, &tmap_b, bar(0), 0, 0, 0);
+      tma_load_3d(B + SUB_BYTES, &tmap_b, bar(0), 64, 0, 0);
+      bool ok = wait_or_abort(bar(0), 0, abort_flag);
+      if (ok) {
+        tc_fence_after();
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t koff = (ks >> 2) * SUB_BYTES + (ks & 3) * 32;
+          umma_ss(tmem, umma_desc(A + koff, 16, 1024), umma_desc(B + koff, 16, 1024), umma_idesc(128, 128, 0, 0), ks > 0);
+        }
+        umma_commit(bar(1));
+        ok = wait_or_abort(bar(2), 0, abort_flag);
+      }
+      if (ok) {
+        tc_fence_after();
+        for (int ks = 0; ks < 8; ++ks)
+          umma_ts(tmem + 128, tmem + ks * 8, umma_desc(B + ks * 2048, SUB_BYTES, 1024), umma_idesc(128, 128, 0, 1), ks > 0);
+        umma_commit(bar(3));
+      }
+    }
+  } else {
+    const int r = warp * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    bool ok = wait_or_abort(bar(1), 0, abort_flag);
+    tc_fence_after();
+    if (ok) {
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem + lane_addr + c * 32, v);
+        tmem_wait_ld();
+        for (int e = 0; e < 32; ++e) out1[r * 128 + c * 32 + e] = __uint_as_float(v[e]);
+      }
+      // stage row r of A as packed bf16 pairs in TMEM columns [0,64)
+      uint32_t pk[64];
+      const uint32_t* arow = reinterpret_cast<const uint32_t*>(a + r * 128);
+      for (int c = 0; c < 64; ++c) pk[c] = arow[c];
+      tmem_st32(tmem + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&pk[0]));
+      tmem_st32(tmem + lane_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&pk[32]));
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(2));
+      ok = wait_or_abort(bar(3), 0, abort_flag);
+      tc_fence_after();
+      if (ok) {
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tmem + 128 + lane_addr + c * 32, v);
+          tmem_wait_ld();
+          for (int e = 0; e < 32; ++e) out2[r * 128 + c * 32 + e] = __uint_as_float(v[e]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0 && *abort_flag) atomicOr(status, NVLLM_STATUS_TIMEOUT);
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------
+
+template <class K>
+static int opt_in_smem(K kernel, int bytes, bool* done, const char* what) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || done[dev]) return NVLLM_OK;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return fail(NVLLM_E_CUDA, "%s: cannot reserve %d bytes of shared memory: %s", what, bytes, cudaGetErrorString(e));
+  done[dev] = true;
+  return NVLLM_OK;
+}
+
+int launch_prefill_tc(const PrefillParams& p, int64_t total_q, int64_t total_k, cudaStream_t stream) {
+  static bool attr_done[64] = {false};
+  int rc = opt_in_smem(prefill_tc_kernel, tc::SMEM, attr_done, "prefill (tcgen05)");
+  if (rc) return rc;
+  CUtensorMap mq, mk, mv;
+  if (!make_tmap_3d(&mq, p.q, tc::D, p.hq, total_q, tc::D, p.q_stride, tc::BM)) return NVLLM_E_CUDA;
+  if (p.block_tables) {
+    const uint64_t slots = static_cast<uint64_t>(p.num_blocks) * kBlockSize;
+    const uint64_t row = static_cast<uint64_t>(p.hkv) * tc::D;
+    if (!make_tmap_3d(&mk, p.k, tc::D, p.hkv, slots, tc::D, row, tc::BN)) return NVLLM_E_CUDA;
+    if (!make_tmap_3d(&mv, p.v, tc::D, p.hkv, slots, tc::D, row, tc::BN)) return NVLLM_E_CUDA;
+  } else {
+    if (!make_tmap_3d(&mk, p.k, tc::D, p.hkv, total_k, tc::D, p.k_stride, tc::BN)) return NVLLM_E_CUDA;
+    if (!make_tmap_3d(&mv, p.v, tc::D, p.hkv, total_k, tc::D, p.v_stride, tc::BN)) return NVLLM_E_CUDA;
+  }
+  dim3 grid((p.max_seqlen_q + tc::BM - 1) / tc::BM, p.hq, p.batch);
+  prefill_tc_kernel<<<grid, tc::NTHREADS, tc::SMEM, stream>>>(p, mq, mk, mv);
+  count_launch();
+  return check_launch("prefill (tcgen05) launch");
+}
+
+}  // namespace nvllm
+
+extern "C" int nvllm_selftest_umma(const void* a, const void* b, float* out_ss, float* out_ts, void* stream) {
+  using namespace nvllm;
+  if (!a || !b || !out_ss || !out_ts) return fail(NVLLM_E_NULL, "selftest_umma: NULL pointer argument");
+  if (!aligned16(a) || !aligned16(b)) return fail(NVLLM_E_ALIGN, "selftest_umma: inputs must be 16-byte aligned");
+  int* status = status_word();
+  if (!status) return fail(NVLLM_E_NO_DEVICE, "selftest_umma: no CUDA device is usable");
+  static bool attr_done[64] = {false};
+  const int smem = 2 * tc::TILE_BYTES + 128 + 1024;
+  int rc = opt_in_smem(umma_selftest_kernel, smem, attr_done, "selftest_umma");
+  if (rc) return rc;
+  CUtensorMap ma, mb;
+  if (!sm100::make_tmap_3d(&ma, a, 128, 1, 128, 128, 128, 128)) return NVLLM_E_CUDA;
+  if (!sm100::make_tmap_3d(&mb, b, 128, 1, 128, 128, 128, 128)) return NVLLM_E_CUDA;
+  umma_selftest_kernel<<<1, 160, smem, static_cast<cudaStream_t>(stream)>>>(
+      ma, mb, static_cast<const __nv_bfloat16*>(a), out_ss, out_ts, status);
+  count_launch();
+  return check_launch("selftest_umma launch");
+}

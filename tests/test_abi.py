@@ -65,14 +65,14 @@ def test_null_and_misaligned_arguments_are_rejected_before_any_launch(lib):
                                 ctypes.c_float(0.1), 100, p16, 1 << 30, None)
     assert rc == -2
     # prefill: NULL cu_seqlens, short stride, paged mode without a table width
-    rc = lib.nvllm_prefill_varlen(p16, 2048, p16, 1024, p16, 1024, None, 0, 0, p16, 2048, None, p16, 2, 100, 100,
+    rc = lib.nvllm_prefill_varlen(p16, 2048, p16, 1024, p16, 1024, None, 0, 0, p16, 2048, None, p16, 200, 200, 2, 100, 100,
                                   16, 8, 128, ctypes.c_float(0.1), 0, None)
     assert rc == -1
-    rc = lib.nvllm_prefill_varlen(p16, 2048, p16, 512, p16, 1024, None, 0, 0, p16, 2048, p16, p16, 2, 100, 100,
+    rc = lib.nvllm_prefill_varlen(p16, 2048, p16, 512, p16, 1024, None, 0, 0, p16, 2048, p16, p16, 200, 200, 2, 100, 100,
                                   16, 8, 128, ctypes.c_float(0.1), 0, None)
     assert rc == -3
-    rc = lib.nvllm_prefill_varlen(p16, 2048, p16, 1024, p16, 1024, p16, 4, 0, p16, 2048, p16, p16, 2, 100, 100,
+    rc = lib.nvllm_prefill_varlen(p16, 2048, p16, 1024, p16, 1024, p16, 4, 0, p16, 2048, p16, p16, 200, 200, 2, 100, 100,
                                   16, 8, 128, ctypes.c_float(0.1), 10, None)
     assert rc == -3
-    assert lib.nvllm_prefill_varlen(p16, 2048, p16, 1024, p16, 1024, None, 0, 0, p16, 2048, p16, p16, 0, 0, 0,
+    assert lib.nvllm_prefill_varlen(p16, 2048, p16, 1024, p16, 1024, None, 0, 0, p16, 2048, p16, p16, 0, 0, 0, 0, 0,
                                     16, 8, 128, ctypes.c_float(0.1), 0, None) == 0  # empty batch
