@@ -4,20 +4,22 @@
 // Math follows the prefill branch of nanovllm/layers/attention.py:67-73
 // (flash_attn_varlen_func, causal, optional block table).
 //
-// One thread block = one 128-row query tile of one (sequence, query head); two blocks are
-// resident per SM (96 KB of shared memory and 256 of the 512 TMEM columns each), so one
-// block's softmax overlaps the other's matrix products.  Six warps with fixed roles:
+// One thread block = one 128-row query tile of one (sequence, query head), walking the keys in
+// 64-token tiles; two blocks are resident per SM (96 KB of shared memory and 256 of the 512
+// TMEM columns each), so one block's softmax overlaps the other's matrix products.  Six warps
+// with fixed roles:
 //   warps 0-3  softmax / correction / epilogue: thread r owns query row r.  It reads its row
 //              of S from TMEM (tcgen05.ld, lane = row, so max and sum need no shuffles),
 //              writes P as packed bf16 back into the same TMEM columns (tcgen05.st) and,
 //              when the running maximum has grown by more than 2^8, rescales its row of O.
-//   warp 4     TMA producer (one lane): Q once, then one K tile and one V tile per step,
-//              each as two 128-row x 64-column boxes with the 128-byte swizzle.
-//   warp 5     MMA issuer (one lane): S = Q K^T (SS form, both operands K-major in shared
-//              memory), then O += P V (TS form: P from TMEM, V as an MN-major shared-memory
-//              operand); completion is signalled to mbarriers with tcgen05.commit.
-// K and V are single-buffered: the K buffer is released when S is complete, the V buffer
-// when O += P V is complete, so the next loads run under the softmax of the current tile.
+//   warp 4     TMA producer (one lane): Q once (two 128-row x 64-column boxes), then one K
+//              tile and one V tile per step (two 64 x 64 boxes each), 128-byte swizzle, into
+//              a two-stage ring.
+//   warp 5     MMA issuer (one lane): S_j = Q K_j^T (SS form, both operands K-major in shared
+//              memory) into one of two S buffers, then O += P_j V_j (TS form: P from TMEM, V
+//              as an MN-major shared-memory operand).  S_{j+1} is issued before P_j V_j so it
+//              runs under the softmax of tile j; completion is signalled to mbarriers with
+//              tcgen05.commit.
 // Every mbarrier wait is bounded; on expiry the block records NVLLM_STATUS_TIMEOUT, all roles
 // leave their loops and TMEM is freed.
 #include "common.cuh"
@@ -28,15 +30,22 @@ namespace nvllm {
 using namespace sm100;
 
 namespace tc {
-constexpr int BM = 128, BN = 128, D = 128;
-constexpr int TILE_BYTES = BM * D * 2;   // 32 KB: two [128 x 64] swizzled sub-tiles
-constexpr int SUB_BYTES = TILE_BYTES / 2;
-constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = 2 * TILE_BYTES, OFF_BAR = 3 * TILE_BYTES;
-constexpr int SMEM = 3 * TILE_BYTES + 256 + 1024;  // + barriers + alignment slack
-constexpr int TMEM_COLS = 256;                      // S/P: columns [0,128), O: [128,256)
+constexpr int BM = 128, BN = 64, D = 128, KST = 2;
+constexpr int Q_BYTES = BM * D * 2;        // 32 KB: two [128 x 64] swizzled sub-tiles
+constexpr int Q_SUB = Q_BYTES / 2;
+constexpr int KV_BYTES = BN * D * 2;       // 16 KB: two [64 x 64] swizzled sub-tiles
+constexpr int KV_SUB = KV_BYTES / 2;
+constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + KST * KV_BYTES, OFF_BAR = OFF_V + KST * KV_BYTES;
+constexpr int SMEM = OFF_BAR + 256 + 1024;  // + barriers + alignment slack
+constexpr int TMEM_COLS = 256;              // S/P buffers: [0,64) and [64,128); O: [128,256)
 constexpr int NTHREADS = 192;
-constexpr float kRescaleThreshold = 8.f;            // log2 units
-enum Bar { Q_FULL = 0, K_FULL, V_FULL, K_EMPTY, V_EMPTY, S_FULL, P_FULL, O_FULL, DRAIN, NUM_BARS };
+constexpr float kRescaleThreshold = 8.f;    // log2 units
+enum Bar {
+  Q_FULL = 0, K_FULL0, K_FULL1, V_FULL0, V_FULL1, K_EMPTY0, K_EMPTY1, V_EMPTY0, V_EMPTY1,
+  S_FULL0, S_FULL1, P_FULL0, P_FULL1, PV_DONE, O_FULL, DRAIN, NUM_BARS
+};
+// self-test tile geometry (128 x 128 operands)
+constexpr int TILE_BYTES = 128 * 128 * 2, SUB_BYTES = TILE_BYTES / 2;
 }  // namespace tc
 
 // Bounded wait that also gives up as soon as another role has aborted.
@@ -81,7 +90,7 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + OFF_BAR + 8 * NUM_BARS + 8);
 
   if (tid == 0) {
-    for (int i = 0; i < NUM_BARS; ++i) mbar_init(bar(i), i == P_FULL ? 128u : 1u);
+    for (int i = 0; i < NUM_BARS; ++i) mbar_init(bar(i), (i == P_FULL0 || i == P_FULL1) ? 4u : 1u);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -90,7 +99,7 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tmem_s = tmem, tmem_o = tmem + 128;
+  const uint32_t tmem_o = tmem + 128;
 
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
@@ -98,11 +107,12 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
       prefetch_tmap(&tmap_q);
       prefetch_tmap(&tmap_k);
       prefetch_tmap(&tmap_v);
-      mbar_expect_tx(bar(Q_FULL), TILE_BYTES);
+      mbar_expect_tx(bar(Q_FULL), Q_BYTES);
       tma_load_3d(base + OFF_Q, &tmap_q, bar(Q_FULL), 0, h, q0 + m0);
-      tma_load_3d(base + OFF_Q + SUB_BYTES, &tmap_q, bar(Q_FULL), 64, h, q0 + m0);
+      tma_load_3d(base + OFF_Q + Q_SUB, &tmap_q, bar(Q_FULL), 64, h, q0 + m0);
       const int32_t* bt_row = p.block_tables ? p.block_tables + b * p.bt_stride : nullptr;
       for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1, use = j >> 1;
         int row;
         if (bt_row) {
           int64_t blk = bt_row[(j * BN) / kBlockSize];
@@ -114,14 +124,14 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
         } else {
           row = k0 + j * BN;
         }
-        if (j > 0 && !wait_or_abort(bar(K_EMPTY), (j - 1) & 1, abort_flag)) break;
-        mbar_expect_tx(bar(K_FULL), TILE_BYTES);
-        tma_load_3d(base + OFF_K, &tmap_k, bar(K_FULL), 0, kvh, row);
-        tma_load_3d(base + OFF_K + SUB_BYTES, &tmap_k, bar(K_FULL), 64, kvh, row);
-        if (j > 0 && !wait_or_abort(bar(V_EMPTY), (j - 1) & 1, abort_flag)) break;
-        mbar_expect_tx(bar(V_FULL), TILE_BYTES);
-        tma_load_3d(base + OFF_V, &tmap_v, bar(V_FULL), 0, kvh, row);
-        tma_load_3d(base + OFF_V + SUB_BYTES, &tmap_v, bar(V_FULL), 64, kvh, row);
+        if (use > 0 && !wait_or_abort(bar(K_EMPTY0 + st), (use - 1) & 1, abort_flag)) break;
+        mbar_expect_tx(bar(K_FULL0 + st), KV_BYTES);
+        tma_load_3d(base + OFF_K + st * KV_BYTES, &tmap_k, bar(K_FULL0 + st), 0, kvh, row);
+        tma_load_3d(base + OFF_K + st * KV_BYTES + KV_SUB, &tmap_k, bar(K_FULL0 + st), 64, kvh, row);
+        if (use > 0 && !wait_or_abort(bar(V_EMPTY0 + st), (use - 1) & 1, abort_flag)) break;
+        mbar_expect_tx(bar(V_FULL0 + st), KV_BYTES);
+        tma_load_3d(base + OFF_V + st * KV_BYTES, &tmap_v, bar(V_FULL0 + st), 0, kvh, row);
+        tma_load_3d(base + OFF_V + st * KV_BYTES + KV_SUB, &tmap_v, bar(V_FULL0 + st), 64, kvh, row);
       }
     }
   } else if (warp == 5) {
@@ -129,27 +139,37 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
     if (lane == 0 && n_kv > 0) {
       constexpr uint32_t idesc_qk = umma_idesc(BM, BN, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc(BM, D, 0, 1);
-      bool ok = wait_or_abort(bar(Q_FULL), 0, abort_flag);
-      for (int j = 0; ok && j < n_kv; ++j) {
-        if (!(ok = wait_or_abort(bar(K_FULL), j & 1, abort_flag))) break;
+      // S_j = Q K_j^T into S buffer j&1
+      auto issue_qk = [&](int j) -> bool {
+        const int st = j & 1;
+        if (!wait_or_abort(bar(K_FULL0 + st), (j >> 1) & 1, abort_flag)) return false;
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t koff = (ks >> 2) * SUB_BYTES + (ks & 3) * 32;
-          umma_ss(tmem_s, umma_desc(base + OFF_Q + koff, 16, 1024), umma_desc(base + OFF_K + koff, 16, 1024),
+          const uint32_t qoff = (ks >> 2) * Q_SUB + (ks & 3) * 32;
+          const uint32_t koff = st * KV_BYTES + (ks >> 2) * KV_SUB + (ks & 3) * 32;
+          umma_ss(tmem + st * 64, umma_desc(base + OFF_Q + qoff, 16, 1024), umma_desc(base + OFF_K + koff, 16, 1024),
                   idesc_qk, ks > 0);
         }
-        umma_commit(bar(S_FULL));
-        umma_commit(bar(K_EMPTY));
-        if (!(ok = wait_or_abort(bar(V_FULL), j & 1, abort_flag))) break;
-        if (!(ok = wait_or_abort(bar(P_FULL), j & 1, abort_flag))) break;
+        umma_commit(bar(S_FULL0 + st));
+        umma_commit(bar(K_EMPTY0 + st));
+        return true;
+      };
+      bool ok = wait_or_abort(bar(Q_FULL), 0, abort_flag);
+      ok = ok && issue_qk(0);
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int st = j & 1, ph = (j >> 1) & 1;
+        if (j + 1 < n_kv && !(ok = issue_qk(j + 1))) break;  // next S runs under this tile's softmax
+        if (!(ok = wait_or_abort(bar(V_FULL0 + st), ph, abort_flag))) break;
+        if (!(ok = wait_or_abort(bar(P_FULL0 + st), ph, abort_flag))) break;
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
-          umma_ts(tmem_o, tmem_s + ks * 8, umma_desc(base + OFF_V + ks * 2048, SUB_BYTES, 1024), idesc_pv,
-                  (j > 0 || ks > 0) ? 1u : 0u);
+          umma_ts(tmem_o, tmem + st * 64 + ks * 8, umma_desc(base + OFF_V + st * KV_BYTES + ks * 2048, KV_SUB, 1024),
+                  idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
         }
-        umma_commit(bar(V_EMPTY));
+        umma_commit(bar(V_EMPTY0 + st));
+        umma_commit(bar(PV_DONE));
         if (j == n_kv - 1) umma_commit(bar(O_FULL));
       }
       if (!ok) {  // make sure nothing is still running on TMEM before it is freed
@@ -165,32 +185,29 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
-      if (!(ok = wait_or_abort(bar(S_FULL), j & 1, abort_flag))) break;
+      const int st = j & 1, ph = (j >> 1) & 1;
+      const uint32_t tmem_s = tmem + st * 64 + lane_addr;
+      if (!(ok = wait_or_abort(bar(S_FULL0 + st), ph, abort_flag))) break;
       tc_fence_after();
-      uint32_t s[128];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s + lane_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+      uint32_t s[64];
+      tmem_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_ld32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
       tmem_wait_ld();
 
       const int j0 = j * BN;
-      const int limit = min(qi + off, Lk - 1) - j0;  // columns c <= limit are visible
-      const bool need_mask = (j0 + BN - 1 > m0 + off) || (j0 + BN > Lk);
-      float mx = -INFINITY;
-      if (need_mask) {
+      if ((j0 + BN - 1 > m0 + off) || (j0 + BN > Lk)) {  // tile touches the diagonal or the end
+        const int limit = min(qi + off, Lk - 1) - j0;      // columns c <= limit are visible
 #pragma unroll
-        for (int c = 0; c < 128; ++c) {
-          float v = __uint_as_float(s[c]);
-          v = (c <= limit) ? v : -INFINITY;
-          s[c] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 128; ++c) mx = fmaxf(mx, __uint_as_float(s[c]));
+        for (int c = 0; c < 64; ++c)
+          if (c > limit) s[c] = 0xff800000u;  // -inf
       }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(s[c]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx * p.scale_log2e);
       // lazy rescale: keep the old reference maximum unless it has been outgrown by 2^8
-      const bool grow = m_new > m_used + kRescaleThreshold || (m_used == -INFINITY && m_new > -INFINITY);
+      const bool grow = m_new > m_used + kRescaleThreshold;
       if (__any_sync(0xffffffffu, grow)) {
         float alpha = 1.f;
         if (grow) {
@@ -198,7 +215,9 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
           m_used = m_new;
           l *= alpha;
         }
-        if (j > 0) {
+        if (j > 0) {  // O holds tiles 0..j-1 once the previous P V product has finished
+          if (!(ok = wait_or_abort(bar(PV_DONE), (j - 1) & 1, abort_flag))) break;
+          tc_fence_after();
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             uint32_t o[32];
@@ -211,20 +230,20 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
         }
       }
       const float msub = (m_used == -INFINITY) ? 0.f : m_used;
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {  // P is packed in place: s[c] <- (p[2c], p[2c+1])
+      for (int c = 0; c < 32; ++c) {  // P is packed in place: s[c] <- (p[2c], p[2c+1])
         const float p0 = fast_exp2(fmaf(__uint_as_float(s[2 * c]), p.scale_log2e, -msub));
         const float p1 = fast_exp2(fmaf(__uint_as_float(s[2 * c + 1]), p.scale_log2e, -msub));
-        sum += p0 + p1;
+        sum4[c & 3] += p0 + p1;
         s[c] = pack_bf16x2(p0, p1);
       }
-      l += sum;
-      tmem_st32(tmem_s + lane_addr, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-      tmem_st32(tmem_s + lane_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      tmem_st32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(P_FULL));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(P_FULL0 + st));
     }
     // epilogue: O / l -> bf16 -> global (rows past the sequence end are not written)
     if (ok && n_kv > 0) ok = wait_or_abort(bar(O_FULL), 0, abort_flag);
