@@ -57,6 +57,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=256, help="sequences in the decode batch")
     ap.add_argument("--no-secondary", action="store_true", help="skip the store/prefill/long-context extras")
+    ap.add_argument("--kernel", default=None, choices=["prefill", "prefill_long", "store", "decode_long"],
+                    help="time only this secondary kernel on one GPU and print its line (profiling aid)")
     return ap.parse_args()
 
 
@@ -336,10 +338,19 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def secondary(dev, hbm_peak_gbs):
-    """Other kernels of the path, 1 GPU, device-timed (median of 20 after 3 warm-ups)."""
+def secondary(dev, hbm_peak_gbs, only=None):
+    """Other kernels of the path, 1 GPU, device-timed (median of 20 after 3 warm-ups, L2
+    flushed between iterations)."""
     import torch
     from nano_vllm_b200 import attention as A, workloads as W
+
+    tf_peak = None
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            tf_peak = float(json.loads(p.read_text())["bf16_tflops"])
+        except Exception:
+            pass
 
     def med(fn, iters=20):
         for _ in range(3):
@@ -354,31 +365,65 @@ def secondary(dev, hbm_peak_gbs):
         torch.cuda.synchronize()
         return statistics.median(a.elapsed_time(b) for a, b in evs)
 
+    def tf_line(ms, fl):
+        d = {"us": round(ms * 1e3, 1), "TFLOP/s": round(fl / ms / 1e9, 1)}
+        if tf_peak:
+            d["frac_of_bf16_peak"] = round(fl / ms / 1e9 / tf_peak, 3)
+        return d
+
     res = {}
-    pc = W.cfg2_prefill(dev)
-    n = pc.k.shape[0]
-    ms = med(lambda: A.store_kvcache(pc.k, pc.v, pc.k_cache, pc.v_cache, pc.slot_mapping))
-    sb = W.store_bytes(n, 8 * 128)
-    res["store_kvcache_cfg2"] = {"us": round(ms * 1e3, 1), "GB/s": round(sb / ms / 1e6, 1), "frac_of_hbm_peak": round(sb / ms / 1e6 / hbm_peak_gbs, 3)}
-    lq = (pc.cu_seqlens_q[1:] - pc.cu_seqlens_q[:-1]).tolist()
-    lk = (pc.cu_seqlens_k[1:] - pc.cu_seqlens_k[:-1]).tolist()
-    fl = W.prefill_flops(lq, lk, 16, 128)
-    o = torch.empty_like(pc.q)
-    ms = med(lambda: A.prefill_varlen(pc.q, pc.k_cache, pc.v_cache, pc.cu_seqlens_q, pc.cu_seqlens_k, pc.max_seqlen_q,
-                                      pc.max_seqlen_k, pc.scale, block_tables=pc.block_tables, out=o))
-    res["prefill_cfg2_paged"] = {"us": round(ms * 1e3, 1), "TFLOP/s": round(fl / ms / 1e9, 1)}
-    del pc, o
-    c5 = W.cfg5_decode(1, dev, batch=256)
-    B, Hq, Hkv, D = c5.geometry
-    nb = W.decode_bytes(c5.context_lens.cpu(), Hq, Hkv, D)
-    o = torch.empty_like(c5.q)
-    ms = med(lambda: A.decode_paged(c5.q, c5.k_cache, c5.v_cache, c5.context_lens, c5.block_tables, c5.scale, out=o), 10)
-    res["decode_cfg5_b256_ctx32768"] = {"us": round(ms * 1e3, 1), "GB/s": round(nb / ms / 1e6, 1), "frac_of_hbm_peak": round(nb / ms / 1e6 / hbm_peak_gbs, 3)}
+    if only in (None, "store", "prefill"):
+        pc = W.cfg2_prefill(dev)
+        n = pc.k.shape[0]
+        if only in (None, "store"):
+            ms = med(lambda: A.store_kvcache(pc.k, pc.v, pc.k_cache, pc.v_cache, pc.slot_mapping))
+            sb = W.store_bytes(n, 8 * 128)
+            res["store_kvcache_cfg2"] = {"us": round(ms * 1e3, 1), "GB/s": round(sb / ms / 1e6, 1),
+                                         "frac_of_hbm_peak": round(sb / ms / 1e6 / hbm_peak_gbs, 3)}
+        if only in (None, "prefill"):
+            A.store_kvcache(pc.k, pc.v, pc.k_cache, pc.v_cache, pc.slot_mapping)
+            lq = (pc.cu_seqlens_q[1:] - pc.cu_seqlens_q[:-1]).tolist()
+            lk = (pc.cu_seqlens_k[1:] - pc.cu_seqlens_k[:-1]).tolist()
+            fl = W.prefill_flops(lq, lk, 16, 128)
+            o = torch.empty_like(pc.q)
+            ms = med(lambda: A.prefill_varlen(pc.q, pc.k_cache, pc.v_cache, pc.cu_seqlens_q, pc.cu_seqlens_k,
+                                              pc.max_seqlen_q, pc.max_seqlen_k, pc.scale,
+                                              block_tables=pc.block_tables, out=o))
+            res["prefill_cfg2_paged"] = tf_line(ms, fl)
+            del o
+        del pc
+    if only in (None, "prefill_long"):
+        # the engine's warm-up shape: 4 sequences of 4096 tokens, packed K/V, Qwen3-0.6B heads
+        pl = W.make_prefill_case(9, 4, 1, 1, 16, 8, 128, device=dev, lengths=[4096] * 4, with_cache=False)
+        fl = W.prefill_flops([4096] * 4, [4096] * 4, 16, 128)
+        o = torch.empty_like(pl.q)
+        ms = med(lambda: A.prefill_varlen(pl.q, pl.k, pl.v, pl.cu_seqlens_q, pl.cu_seqlens_k, 4096, 4096, pl.scale, out=o))
+        res["prefill_4x4096_packed"] = tf_line(ms, fl)
+        del pl, o
+    if only in (None, "decode_long"):
+        c5 = W.cfg5_decode(1, dev, batch=256)
+        B, Hq, Hkv, D = c5.geometry
+        nb = W.decode_bytes(c5.context_lens.cpu(), Hq, Hkv, D)
+        o = torch.empty_like(c5.q)
+        ms = med(lambda: A.decode_paged(c5.q, c5.k_cache, c5.v_cache, c5.context_lens, c5.block_tables, c5.scale, out=o), 10)
+        res["decode_cfg5_b256_ctx32768"] = {"us": round(ms * 1e3, 1), "GB/s": round(nb / ms / 1e6, 1),
+                                            "frac_of_hbm_peak": round(nb / ms / 1e6 / hbm_peak_gbs, 3)}
     return res
+
+
+def run_one_kernel(args):
+    import torch
+    from nano_vllm_b200 import build as _build
+    _build.build()
+    torch.cuda.set_device(0)
+    peak, _ = hbm_peak()
+    print(json.dumps({"kernel": args.kernel, **secondary(torch.device("cuda", 0), peak, only=args.kernel)}), flush=True)
 
 
 def main():
     args = parse_args()
+    if args.kernel:
+        return run_one_kernel(args)
     if args.impl == "reference":
         run_reference(args)
     else:

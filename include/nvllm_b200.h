@@ -155,8 +155,8 @@ NVLLM_API int nvllm_decode_paged_static(const void* q, int64_t q_row_stride,
  * q/out: [total_q, Hq, D] with the given row strides.  Lq_b == 0 is legal (no work).
  * total_q / total_k are the row counts of q and of packed k/v (ignored for k/v in paged
  * mode); they bound the tiled loads, nothing past them is read.
- * Supported: D in {64,128}; Hq % Hkv == 0.  D == 128 runs on the tcgen05 kernel, which
- * needs every K/V row the table or cu_seqlens_k makes visible to hold finite values.
+ * Cache contents past a sequence's length are never observed (stale NaN/Inf cannot leak).
+ * Supported: D in {64,128}; Hq % Hkv == 0.  D == 128 runs on the tcgen05 kernel.
  */
 NVLLM_API int nvllm_prefill_varlen(const void* q, int64_t q_row_stride,
                          const void* k, int64_t k_row_stride,

@@ -239,6 +239,19 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
         s[c] = pack_bf16x2(p0, p1);
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      if (j0 + BN > Lk) {
+        // Last tile of the sequence: V rows past the end hold whatever the cache block (or the
+        // next sequence) has there.  Their P is 0, but 0 x NaN would still poison O, so the
+        // rows are cleared in shared memory before the product is issued.
+        if (!(ok = wait_or_abort(bar(V_FULL0 + st), ph, abort_flag))) break;
+        const int first = Lk - j0;  // rows [first, 64) are dead
+        unsigned char* vt = base_ptr + OFF_V + st * KV_BYTES;
+        for (int i = r; i < (BN - first) * 16; i += 128) {
+          const int row = first + (i >> 4), piece = i & 15;
+          *reinterpret_cast<uint4*>(vt + (piece >> 3) * KV_SUB + row * 128 + (piece & 7) * 16) = make_uint4(0, 0, 0, 0);
+        }
+        fence_proxy_async();
+      }
       tmem_st32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       tmem_wait_st();
       tc_fence_before();

@@ -73,3 +73,13 @@ def test_strided_v_view(cuda):
     out = A.prefill_varlen(qd, kd, vd, cu.to(cuda), cu.to(cuda), 400, 400, d ** -0.5)
     ref = R.prefill_ref(q, k, v, cu, cu, d ** -0.5)
     assert_close_to_oracle(out, ref, "strided")
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_stale_cache_rows_past_the_sequence_cannot_leak(cuda, d):
+    """A partly filled last block holds NaN/Inf past the sequence end; outputs stay finite."""
+    case = W.make_prefill_case(25, 3, 1, 1, 8, 2, d, lengths=[300, 700, 513], shared_blocks=[0, 1, 2])
+    assert case.block_tables is not None
+    case.k_cache[:] = float("nan")
+    case.v_cache[:] = float("inf")
+    _check(cuda, case, f"stale d{d}")
