@@ -9,7 +9,11 @@ import ctypes
 from ctypes import c_char_p, c_float, c_int32, c_int64, c_void_p, POINTER
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libnvllm_b200.so"
+import os
+
+# NVLLM_B200_LIB points the loader at another build of the same library (e.g. one compiled
+# with development instrumentation); by default the in-tree build is used.
+LIB_PATH = Path(os.environ.get("NVLLM_B200_LIB") or Path(__file__).resolve().parent / "libnvllm_b200.so")
 
 # name -> (restype, argtypes); mirrors include/nvllm_b200.h one to one
 SIGNATURES = {

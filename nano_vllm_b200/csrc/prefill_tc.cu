@@ -22,6 +22,8 @@
 //              tcgen05.commit.
 // Every mbarrier wait is bounded; on expiry the block records NVLLM_STATUS_TIMEOUT, all roles
 // leave their loops and TMEM is freed.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "prefill.cuh"
 #include "sm100.cuh"
@@ -40,13 +42,31 @@ constexpr int SMEM = OFF_BAR + 256 + 1024;  // + barriers + alignment slack
 constexpr int TMEM_COLS = 256;              // S/P buffers: [0,64) and [64,128); O: [128,256)
 constexpr int NTHREADS = 192;
 constexpr float kRescaleThreshold = 8.f;    // log2 units
+// One tcgen05.commit per MMA group: a commit that follows a group of a different kind costs the
+// tensor pipe a bubble (~100-200 cycles measured), so each completion is signalled once and
+// shared by all its waiters.  QK_DONE[s]: S buffer s holds S_j (softmax) and K stage s is free
+// (producer).  PV_DONE[s]: V stage s is free (producer), O includes tile j (rescale, epilogue).
 enum Bar {
-  Q_FULL = 0, K_FULL0, K_FULL1, V_FULL0, V_FULL1, K_EMPTY0, K_EMPTY1, V_EMPTY0, V_EMPTY1,
-  S_FULL0, S_FULL1, P_FULL0, P_FULL1, PV_DONE, O_FULL, DRAIN, NUM_BARS
+  Q_FULL = 0, K_FULL0, K_FULL1, V_FULL0, V_FULL1, QK_DONE0, QK_DONE1, PV_DONE0, PV_DONE1,
+  P_FULL0, P_FULL1, DRAIN, NUM_BARS
 };
 // self-test tile geometry (128 x 128 operands)
 constexpr int TILE_BYTES = 128 * 128 * 2, SUB_BYTES = TILE_BYTES / 2;
 }  // namespace tc
+
+#ifdef NVLLM_PHASE_CLOCKS
+// Development aid: per-tile clock64() stamps of one block's softmax thread 0 and MMA thread.
+__device__ long long g_phase_clocks[64 * 12];
+__device__ int g_dev_mode = 0;  // 1: softmax does no TMEM traffic and no math; 2: TMEM traffic only
+#define PHASE_STAMP(j, k)                                                    \
+  do {                                                                       \
+    if (prof_block && (j) < 64) g_phase_clocks[(j) * 12 + (k)] = clock64();  \
+  } while (0)
+#else
+#define PHASE_STAMP(j, k) \
+  do {                    \
+  } while (0)
+#endif
 
 // Bounded wait that also gives up as soon as another role has aborted.
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
@@ -82,6 +102,9 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
   if (kv_end < 0) kv_end = 0;
   const int n_kv = (kv_end + BN - 1) / BN;
 
+#ifdef NVLLM_PHASE_CLOCKS
+  const bool prof_block = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid == 0 || tid == 160);
+#endif
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bars = base + OFF_BAR;
@@ -124,11 +147,11 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
         } else {
           row = k0 + j * BN;
         }
-        if (use > 0 && !wait_or_abort(bar(K_EMPTY0 + st), (use - 1) & 1, abort_flag)) break;
+        if (use > 0 && !wait_or_abort(bar(QK_DONE0 + st), (use - 1) & 1, abort_flag)) break;
         mbar_expect_tx(bar(K_FULL0 + st), KV_BYTES);
         tma_load_3d(base + OFF_K + st * KV_BYTES, &tmap_k, bar(K_FULL0 + st), 0, kvh, row);
         tma_load_3d(base + OFF_K + st * KV_BYTES + KV_SUB, &tmap_k, bar(K_FULL0 + st), 64, kvh, row);
-        if (use > 0 && !wait_or_abort(bar(V_EMPTY0 + st), (use - 1) & 1, abort_flag)) break;
+        if (use > 0 && !wait_or_abort(bar(PV_DONE0 + st), (use - 1) & 1, abort_flag)) break;
         mbar_expect_tx(bar(V_FULL0 + st), KV_BYTES);
         tma_load_3d(base + OFF_V + st * KV_BYTES, &tmap_v, bar(V_FULL0 + st), 0, kvh, row);
         tma_load_3d(base + OFF_V + st * KV_BYTES + KV_SUB, &tmap_v, bar(V_FULL0 + st), 64, kvh, row);
@@ -139,38 +162,47 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
     if (lane == 0 && n_kv > 0) {
       constexpr uint32_t idesc_qk = umma_idesc(BM, BN, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc(BM, D, 0, 1);
+      // Descriptors are built once; inside the loops only their 14-bit address field moves
+      // (a 64-bit add of a compile-time constant), so the single issuing thread spends a few
+      // instructions per MMA instead of rebuilding 64-bit descriptors.
+      const uint64_t q_desc = umma_desc(base + OFF_Q, 16, 1024);
+      const uint64_t k_desc = umma_desc(base + OFF_K, 16, 1024);      // stage 0; stage 1 = + KV_BYTES
+      const uint64_t v_desc = umma_desc(base + OFF_V, KV_SUB, 1024);
       // S_j = Q K_j^T into S buffer j&1
       auto issue_qk = [&](int j) -> bool {
         const int st = j & 1;
         if (!wait_or_abort(bar(K_FULL0 + st), (j >> 1) & 1, abort_flag)) return false;
+        PHASE_STAMP(j - 1, 10);
         tc_fence_after();
+        const uint64_t kd = k_desc + static_cast<uint64_t>(st * (KV_BYTES >> 4));
+        const uint32_t d_tmem = tmem + st * 64;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t qoff = (ks >> 2) * Q_SUB + (ks & 3) * 32;
-          const uint32_t koff = st * KV_BYTES + (ks >> 2) * KV_SUB + (ks & 3) * 32;
-          umma_ss(tmem + st * 64, umma_desc(base + OFF_Q + qoff, 16, 1024), umma_desc(base + OFF_K + koff, 16, 1024),
-                  idesc_qk, ks > 0);
+          const uint64_t qoff = ((ks >> 2) * Q_SUB + (ks & 3) * 32) >> 4;
+          const uint64_t koff = ((ks >> 2) * KV_SUB + (ks & 3) * 32) >> 4;
+          umma_ss(d_tmem, q_desc + qoff, kd + koff, idesc_qk, ks > 0);
         }
-        umma_commit(bar(S_FULL0 + st));
-        umma_commit(bar(K_EMPTY0 + st));
+        umma_commit(bar(QK_DONE0 + st));
         return true;
       };
       bool ok = wait_or_abort(bar(Q_FULL), 0, abort_flag);
       ok = ok && issue_qk(0);
       for (int j = 0; ok && j < n_kv; ++j) {
         const int st = j & 1, ph = (j >> 1) & 1;
+        PHASE_STAMP(j, 9);
         if (j + 1 < n_kv && !(ok = issue_qk(j + 1))) break;  // next S runs under this tile's softmax
+        PHASE_STAMP(j, 6);
         if (!(ok = wait_or_abort(bar(V_FULL0 + st), ph, abort_flag))) break;
         if (!(ok = wait_or_abort(bar(P_FULL0 + st), ph, abort_flag))) break;
+        PHASE_STAMP(j, 7);
         tc_fence_after();
+        const uint64_t vd = v_desc + static_cast<uint64_t>(st * (KV_BYTES >> 4));
+        const uint32_t p_tmem = tmem + st * 64;
 #pragma unroll
-        for (int ks = 0; ks < BN / 16; ++ks) {
-          umma_ts(tmem_o, tmem + st * 64 + ks * 8, umma_desc(base + OFF_V + st * KV_BYTES + ks * 2048, KV_SUB, 1024),
-                  idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
-        }
-        umma_commit(bar(V_EMPTY0 + st));
-        umma_commit(bar(PV_DONE));
-        if (j == n_kv - 1) umma_commit(bar(O_FULL));
+        for (int ks = 0; ks < BN / 16; ++ks)
+          umma_ts(tmem_o, p_tmem + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+        umma_commit(bar(PV_DONE0 + st));
+        PHASE_STAMP(j, 8);
       }
       if (!ok) {  // make sure nothing is still running on TMEM before it is freed
         umma_commit(bar(DRAIN));
@@ -187,12 +219,35 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
     for (int j = 0; j < n_kv; ++j) {
       const int st = j & 1, ph = (j >> 1) & 1;
       const uint32_t tmem_s = tmem + st * 64 + lane_addr;
-      if (!(ok = wait_or_abort(bar(S_FULL0 + st), ph, abort_flag))) break;
+      PHASE_STAMP(j, 0);
+      if (!(ok = wait_or_abort(bar(QK_DONE0 + st), ph, abort_flag))) break;
+      PHASE_STAMP(j, 1);
       tc_fence_after();
+#ifdef NVLLM_PHASE_CLOCKS
+      if (g_dev_mode == 1) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(P_FULL0 + st));
+        continue;
+      }
+      if (g_dev_mode == 2) {
+        uint32_t t[32];
+        tmem_ld32(tmem_s, t);
+        tmem_ld32(tmem_s + 32, t);
+        tmem_wait_ld();
+        tmem_st32(tmem_s, t);
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(P_FULL0 + st));
+        continue;
+      }
+#endif
       uint32_t s[64];
       tmem_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       tmem_ld32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
       tmem_wait_ld();
+      PHASE_STAMP(j, 2);
 
       const int j0 = j * BN;
       if ((j0 + BN - 1 > m0 + off) || (j0 + BN > Lk)) {  // tile touches the diagonal or the end
@@ -216,7 +271,7 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
           l *= alpha;
         }
         if (j > 0) {  // O holds tiles 0..j-1 once the previous P V product has finished
-          if (!(ok = wait_or_abort(bar(PV_DONE), (j - 1) & 1, abort_flag))) break;
+          if (!(ok = wait_or_abort(bar(PV_DONE0 + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag))) break;
           tc_fence_after();
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
@@ -229,6 +284,7 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
           }
         }
       }
+      PHASE_STAMP(j, 3);
       const float msub = (m_used == -INFINITY) ? 0.f : m_used;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -252,14 +308,16 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
         }
         fence_proxy_async();
       }
+      PHASE_STAMP(j, 4);
       tmem_st32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(P_FULL0 + st));
+      PHASE_STAMP(j, 5);
     }
     // epilogue: O / l -> bf16 -> global (rows past the sequence end are not written)
-    if (ok && n_kv > 0) ok = wait_or_abort(bar(O_FULL), 0, abort_flag);
+    if (ok && n_kv > 0) ok = wait_or_abort(bar(PV_DONE0 + ((n_kv - 1) & 1)), ((n_kv - 1) >> 1) & 1, abort_flag);
     tc_fence_after();
     const float inv = (ok && l > 0.f) ? 1.f / l : 0.f;
     __nv_bfloat16* dst = p.out + static_cast<int64_t>(q0 + qi) * p.out_stride + h * D;
@@ -423,12 +481,27 @@ int launch_prefill_tc(const PrefillParams& p, int64_t total_q, int64_t total_k, 
     if (!make_tmap_3d(&mv, p.v, tc::D, p.hkv, total_k, tc::D, p.v_stride, tc::BN)) return NVLLM_E_CUDA;
   }
   dim3 grid((p.max_seqlen_q + tc::BM - 1) / tc::BM, p.hq, p.batch);
+#ifdef NVLLM_PHASE_CLOCKS
+  static const int pad = std::getenv("NVLLM_TC_SMEM_PAD") ? std::atoi(std::getenv("NVLLM_TC_SMEM_PAD")) : 0;
+  static const int mode = std::getenv("NVLLM_TC_MODE") ? std::atoi(std::getenv("NVLLM_TC_MODE")) : 0;
+  cudaMemcpyToSymbol(g_dev_mode, &mode, sizeof(int));
+  if (pad) cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM + pad);
+  prefill_tc_kernel<<<grid, tc::NTHREADS, tc::SMEM + pad, stream>>>(p, mq, mk, mv);
+  count_launch();
+  return check_launch("prefill (tcgen05) launch");
+#endif
   prefill_tc_kernel<<<grid, tc::NTHREADS, tc::SMEM, stream>>>(p, mq, mk, mv);
   count_launch();
   return check_launch("prefill (tcgen05) launch");
 }
 
 }  // namespace nvllm
+
+#ifdef NVLLM_PHASE_CLOCKS
+extern "C" __attribute__((visibility("default"))) int nvllm_debug_phase_clocks(long long* host_out) {
+  return cudaMemcpyFromSymbol(host_out, nvllm::g_phase_clocks, sizeof(long long) * 64 * 12) == cudaSuccess ? 0 : -5;
+}
+#endif
 
 extern "C" int nvllm_selftest_umma(const void* a, const void* b, float* out_ss, float* out_ts, void* stream) {
   using namespace nvllm;
