@@ -19,19 +19,26 @@ MODULE_NAME = "nanovllm.layers.attention"
 
 
 def install() -> types.ModuleType:
-    late = [m for m in ("nanovllm.models.qwen3", "nanovllm.models.qwen2") if m in sys.modules]
-    if late and getattr(sys.modules.get(MODULE_NAME), "__nano_vllm_b200__", False) is False:
-        raise RuntimeError(f"install() must run before {late[0]} is imported")
-    ctx = importlib.import_module("nanovllm.utils.context")
-    _attention.use_context_getter(ctx.get_context)
+    already = sys.modules.get(MODULE_NAME)
+    if already is not None and getattr(already, "__nano_vllm_b200__", False):
+        return already
+    if already is not None or any(m in sys.modules for m in ("nanovllm.models.qwen3", "nanovllm.models.qwen2")):
+        raise RuntimeError("install() must run before anything of nanovllm is imported: importing the "
+                           "package pulls in its models, which bind Attention at import time")
     mod = types.ModuleType(MODULE_NAME)
     mod.__doc__ = "nano-vllm attention layer backed by libnvllm_b200.so"
     mod.Attention = _attention.Attention
     mod.store_kvcache = _attention.store_kvcache
-    mod.get_context = ctx.get_context
     mod.__nano_vllm_b200__ = True
-    sys.modules[MODULE_NAME] = mod
+    sys.modules[MODULE_NAME] = mod  # registered first: `import nanovllm` below already imports the models
+    ctx = importlib.import_module("nanovllm.utils.context")
+    _attention.use_context_getter(ctx.get_context)
+    mod.get_context = ctx.get_context
     layers = sys.modules.get("nanovllm.layers")
     if layers is not None:
         setattr(layers, "attention", mod)
+    for name in ("nanovllm.models.qwen3", "nanovllm.models.qwen2"):
+        m = sys.modules.get(name)
+        if m is not None and getattr(m, "Attention", None) is not _attention.Attention:
+            raise RuntimeError(f"{name} bound another Attention class; the swap did not take effect")
     return mod
