@@ -86,10 +86,13 @@ def apply_shims(attn: str, ref_path: str):
     mr.load_model = random_init
 
 
-def _worker(config, rank, event, attn, ref_path):
+def _worker(config_blob, rank, event, attn, ref_path):
+    # The config travels as bytes: unpickling a nanovllm object would import the package (and
+    # with it the stock attention module) before the swap below has been made.
     apply_shims(attn, ref_path)
+    import pickle
     from nanovllm.engine.model_runner import ModelRunner
-    ModelRunner(config, rank, event)
+    ModelRunner(pickle.loads(config_blob), rank, event)
 
 
 def make_engine(model_dir: str, attn: str, ref_path: str, **kwargs):
@@ -110,9 +113,11 @@ def make_engine(model_dir: str, attn: str, ref_path: str, **kwargs):
             config.hf_config.rope_scaling = None
             self.ps, self.events = [], []
             ctx = mp.get_context("spawn")
+            import pickle
+            blob = pickle.dumps(config)
             for i in range(1, config.tensor_parallel_size):
                 event = ctx.Event()
-                proc = ctx.Process(target=_worker, args=(config, i, event, attn, ref_path))
+                proc = ctx.Process(target=_worker, args=(blob, i, event, attn, ref_path))
                 proc.start()
                 self.ps.append(proc)
                 self.events.append(event)
