@@ -112,10 +112,47 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + OFF_BAR + 8 * NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + OFF_BAR + 8 * NUM_BARS + 8);
 
-  if (tid == 0) {
+  PHASE_STAMP(63, 0);
+  // Loads of K/V tile j into ring stage j&1 (producer lane only).
+  const int32_t* bt_row = p.block_tables ? p.block_tables + b * p.bt_stride : nullptr;
+  auto kv_row = [&](int j) -> int {
+    if (!bt_row) return k0 + j * BN;
+    int64_t blk = bt_row[(j * BN) / kBlockSize];
+    if (blk < 0 || blk >= p.num_blocks) {
+      atomicOr(p.status, NVLLM_STATUS_BAD_BLOCK);
+      blk = 0;
+    }
+    return static_cast<int>(blk * kBlockSize + (j * BN) % kBlockSize);
+  };
+  auto issue_k = [&](int j, int row) {
+    const int st = j & 1;
+    mbar_expect_tx(bar(K_FULL0 + st), KV_BYTES);
+    tma_load_3d(base + OFF_K + st * KV_BYTES, &tmap_k, bar(K_FULL0 + st), 0, kvh, row);
+    tma_load_3d(base + OFF_K + st * KV_BYTES + KV_SUB, &tmap_k, bar(K_FULL0 + st), 64, kvh, row);
+  };
+  auto issue_v = [&](int j, int row) {
+    const int st = j & 1;
+    mbar_expect_tx(bar(V_FULL0 + st), KV_BYTES);
+    tma_load_3d(base + OFF_V + st * KV_BYTES, &tmap_v, bar(V_FULL0 + st), 0, kvh, row);
+    tma_load_3d(base + OFF_V + st * KV_BYTES + KV_SUB, &tmap_v, bar(V_FULL0 + st), 64, kvh, row);
+  };
+  if (warp == 4 && lane == 0) {
+    // The producer lane sets up the barriers itself and starts the first loads (Q and both
+    // ring stages need no hand-shake) before the block-wide sync, so their latency overlaps
+    // the TMEM allocation and the other warps' start-up.
     for (int i = 0; i < NUM_BARS; ++i) mbar_init(bar(i), (i == P_FULL0 || i == P_FULL1) ? 4u : 1u);
     *abort_flag = 0;
     mbar_fence_init();
+    if (n_kv > 0) {
+      mbar_expect_tx(bar(Q_FULL), Q_BYTES);
+      tma_load_3d(base + OFF_Q, &tmap_q, bar(Q_FULL), 0, h, q0 + m0);
+      tma_load_3d(base + OFF_Q + Q_SUB, &tmap_q, bar(Q_FULL), 64, h, q0 + m0);
+      for (int j = 0; j < 2 && j < n_kv; ++j) {
+        const int row = kv_row(j);
+        issue_k(j, row);
+        issue_v(j, row);
+      }
+    }
   }
   if (warp == 5) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
   tc_fence_before();
@@ -123,38 +160,19 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tmem_o = tmem + 128;
+  PHASE_STAMP(63, 1);
 
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0 && n_kv > 0) {
-      prefetch_tmap(&tmap_q);
-      prefetch_tmap(&tmap_k);
-      prefetch_tmap(&tmap_v);
-      mbar_expect_tx(bar(Q_FULL), Q_BYTES);
-      tma_load_3d(base + OFF_Q, &tmap_q, bar(Q_FULL), 0, h, q0 + m0);
-      tma_load_3d(base + OFF_Q + Q_SUB, &tmap_q, bar(Q_FULL), 64, h, q0 + m0);
-      const int32_t* bt_row = p.block_tables ? p.block_tables + b * p.bt_stride : nullptr;
-      for (int j = 0; j < n_kv; ++j) {
+    if (lane == 0) {
+      for (int j = 2; j < n_kv; ++j) {
         const int st = j & 1, use = j >> 1;
-        int row;
-        if (bt_row) {
-          int64_t blk = bt_row[(j * BN) / kBlockSize];
-          if (blk < 0 || blk >= p.num_blocks) {
-            atomicOr(p.status, NVLLM_STATUS_BAD_BLOCK);
-            blk = 0;
-          }
-          row = static_cast<int>(blk * kBlockSize + (j * BN) % kBlockSize);
-        } else {
-          row = k0 + j * BN;
-        }
-        if (use > 0 && !wait_or_abort(bar(QK_DONE0 + st), (use - 1) & 1, abort_flag)) break;
-        mbar_expect_tx(bar(K_FULL0 + st), KV_BYTES);
-        tma_load_3d(base + OFF_K + st * KV_BYTES, &tmap_k, bar(K_FULL0 + st), 0, kvh, row);
-        tma_load_3d(base + OFF_K + st * KV_BYTES + KV_SUB, &tmap_k, bar(K_FULL0 + st), 64, kvh, row);
-        if (use > 0 && !wait_or_abort(bar(PV_DONE0 + st), (use - 1) & 1, abort_flag)) break;
-        mbar_expect_tx(bar(V_FULL0 + st), KV_BYTES);
-        tma_load_3d(base + OFF_V + st * KV_BYTES, &tmap_v, bar(V_FULL0 + st), 0, kvh, row);
-        tma_load_3d(base + OFF_V + st * KV_BYTES + KV_SUB, &tmap_v, bar(V_FULL0 + st), 64, kvh, row);
+        // K stage free once S_{j-2} is complete, V stage free once P_{j-2} V_{j-2} is complete
+        const int row = kv_row(j);
+        if (!wait_or_abort(bar(QK_DONE0 + st), (use - 1) & 1, abort_flag)) break;
+        issue_k(j, row);
+        if (!wait_or_abort(bar(PV_DONE0 + st), (use - 1) & 1, abort_flag)) break;
+        issue_v(j, row);
       }
     }
   } else if (warp == 5) {
@@ -186,7 +204,9 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
         return true;
       };
       bool ok = wait_or_abort(bar(Q_FULL), 0, abort_flag);
+      PHASE_STAMP(63, 2);
       ok = ok && issue_qk(0);
+      PHASE_STAMP(63, 3);
       for (int j = 0; ok && j < n_kv; ++j) {
         const int st = j & 1, ph = (j >> 1) & 1;
         PHASE_STAMP(j, 9);
@@ -316,11 +336,14 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
       if (lane == 0) mbar_arrive(bar(P_FULL0 + st));
       PHASE_STAMP(j, 5);
     }
+    PHASE_STAMP(63, 4);
     // epilogue: O / l -> bf16 -> global (rows past the sequence end are not written)
     if (ok && n_kv > 0) ok = wait_or_abort(bar(PV_DONE0 + ((n_kv - 1) & 1)), ((n_kv - 1) >> 1) & 1, abort_flag);
     tc_fence_after();
     const float inv = (ok && l > 0.f) ? 1.f / l : 0.f;
-    __nv_bfloat16* dst = p.out + static_cast<int64_t>(q0 + qi) * p.out_stride + h * D;
+    // O / l -> bf16, staged through the Q buffer (free now) so that the global stores are
+    // whole 256-byte rows per half warp instead of 32 scattered 16-byte pieces.
+    unsigned char* stage = base_ptr + OFF_Q;
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       uint32_t o[32];
@@ -331,27 +354,42 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
 #pragma unroll
         for (int e = 0; e < 32; ++e) o[e] = 0u;
       }
-      if (qi < Lq) {
 #pragma unroll
-        for (int e = 0; e < 32; e += 8) {
-          uint4 v;
-          v.x = pack_bf16x2(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
-          v.y = pack_bf16x2(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
-          v.z = pack_bf16x2(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
-          v.w = pack_bf16x2(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
-          *reinterpret_cast<uint4*>(dst + c * 32 + e) = v;
-        }
+      for (int k = 0; k < 4; ++k) {
+        uint4 v;
+        v.x = pack_bf16x2(__uint_as_float(o[8 * k]) * inv, __uint_as_float(o[8 * k + 1]) * inv);
+        v.y = pack_bf16x2(__uint_as_float(o[8 * k + 2]) * inv, __uint_as_float(o[8 * k + 3]) * inv);
+        v.z = pack_bf16x2(__uint_as_float(o[8 * k + 4]) * inv, __uint_as_float(o[8 * k + 5]) * inv);
+        v.w = pack_bf16x2(__uint_as_float(o[8 * k + 6]) * inv, __uint_as_float(o[8 * k + 7]) * inv);
+        const int cc = c * 4 + k;  // 16-byte piece of the row
+        *reinterpret_cast<uint4*>(stage + r * 256 + ((cc ^ (r & 15)) << 4)) = v;
       }
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");  // the four softmax warps only
+    __nv_bfloat16* out_tile = p.out + static_cast<int64_t>(q0 + m0) * p.out_stride + h * D;
+    const int rows_valid = min(BM, Lq - m0);
+#pragma unroll 4
+    for (int idx = r; idx < BM * 16; idx += 128) {
+      const int row = idx >> 4, cc = idx & 15;
+      if (row < rows_valid)
+        *reinterpret_cast<uint4*>(out_tile + static_cast<int64_t>(row) * p.out_stride + cc * 8) =
+            *reinterpret_cast<const uint4*>(stage + row * 256 + ((cc ^ (row & 15)) << 4));
     }
   }
 
+  PHASE_STAMP(63, 5);
   tc_fence_before();
   __syncthreads();
+  PHASE_STAMP(63, 6);
   if (tid == 0 && *abort_flag) atomicOr(p.status, NVLLM_STATUS_TIMEOUT);
   if (warp == 5) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
+  PHASE_STAMP(63, 7);
+#ifdef NVLLM_PHASE_CLOCKS
+  if (prof_block && tid == 0) g_phase_clocks[63 * 12 + 8] = n_kv;
+#endif
 }
 
 // ---- known-answer check of the building blocks --------------------------------------------
