@@ -29,5 +29,8 @@ struct PrefillParams {
 int launch_prefill_mma(const PrefillParams& p, cudaStream_t stream);
 // tcgen05 / TMEM / TMA kernel: head_dim 128.  total_q / total_k bound the tiled loads.
 int launch_prefill_tc(const PrefillParams& p, int64_t total_q, int64_t total_k, cudaStream_t stream);
+// Same pipeline in persistent blocks that pull (sequence, query tile, head) items from a global
+// counter; batch <= 1024.
+int launch_prefill_tcp(const PrefillParams& p, int64_t total_q, int64_t total_k, cudaStream_t stream);
 
 }  // namespace nvllm

@@ -1,0 +1,443 @@
+// Persistent variant of the tcgen05 prefill kernel (head_dim 128).
+//
+// Same tile pipeline as prefill_tc.cu (128 query rows x 64-key tiles, S double-buffered in
+// TMEM, P fed back from TMEM, two-stage K/V ring, one commit per MMA group), but a thread
+// block does not end with its query tile: two blocks per SM stay resident for the whole launch,
+// keep their TMEM allocation and barriers, and pull work items (sequence, query tile, head)
+// from a global counter.  What this buys on short prompts, where a block only has a handful of
+// key tiles: the block launch / TMEM allocation / barrier set-up is paid once, the producer
+// lane fetches the next item and starts its Q and first K loads while the current item is
+// still in its last softmax, and the tensor pipe runs the next item's first S product under
+// the current item's epilogue.
+//
+// Item hand-off: the producer lane decodes an item into one of two descriptor slots in shared
+// memory (ITEM_FULL / ITEM_FREE barriers).  All rings keep running across items: tile t of the
+// block's life uses stage t&1 and barrier phase (t>>1)&1.  The epilogue stages O through the
+// V ring (free once the item's last P V product is complete), so the producer holds back only
+// the next item's first two V tiles (STAGE_FREE); the first P V product of an item waits
+// for the previous item's O to be read (O_FREE).
+#include <atomic>
+#include <cstdlib>
+
+#include "common.cuh"
+#include "prefill.cuh"
+#include "prefill_tc.cuh"
+#include "sm100.cuh"
+
+namespace nvllm {
+using namespace sm100;
+
+namespace tcp {
+using namespace tc;
+constexpr int MAX_BATCH = 1024;  // prefix array of query tiles per sequence lives in shared memory
+enum PBar {
+  ITEM_FULL0 = tc::NUM_BARS, ITEM_FULL1, ITEM_FREE0, ITEM_FREE1, O_FREE, STAGE_FREE, P_NUM_BARS
+};
+constexpr int OFF_CTRL = OFF_BAR;                 // barriers (8 B each)
+constexpr int OFF_SLOTS = OFF_CTRL + 256;         // two item descriptors of 8 ints
+constexpr int OFF_MISC = OFF_SLOTS + 64;          // tmem address, abort flag
+constexpr int OFF_PREFIX = OFF_MISC + 64;         // (MAX_BATCH + 1) ints
+constexpr int SMEM = OFF_PREFIX + (MAX_BATCH + 1) * 4 + 60 + 1024;
+constexpr int NUM_SLOTS = 64;                     // launches that may be in flight at once
+static_assert(P_NUM_BARS * 8 <= 256, "barrier area");
+}  // namespace tcp
+
+// Work counters, one pair per launch slot; the last block of a launch to leave resets its pair.
+__device__ unsigned int g_item_counter[tcp::NUM_SLOTS];
+__device__ unsigned int g_done_counter[tcp::NUM_SLOTS];
+
+struct Item {
+  int b, h, m0, q0, Lq, k0, Lk, n_kv;  // n_kv < 0: no more work
+};
+
+__global__ void __launch_bounds__(tc::NTHREADS, 2)
+prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tmap_q,
+                   const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+                   const int counter_slot) {
+  using namespace tcp;
+  extern __shared__ unsigned char smem_raw[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + OFF_CTRL;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  volatile int* slots = reinterpret_cast<volatile int*>(base_ptr + OFF_SLOTS);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + OFF_MISC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + OFF_MISC + 8);
+  int* prefix = reinterpret_cast<int*>(base_ptr + OFF_PREFIX);  // prefix[b] = query tiles before sequence b
+
+  if (warp == 4) {
+    // query tiles per sequence -> exclusive prefix sum (warp scan, 32 sequences at a time)
+    int carry = 0;
+    for (int b0 = 0; b0 < p.batch; b0 += 32) {
+      const int b = b0 + lane;
+      int tiles = 0;
+      if (b < p.batch) tiles = (p.cu_q[b + 1] - p.cu_q[b] + BM - 1) / BM;
+      int incl = tiles;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += v;
+      }
+      if (b < p.batch) prefix[b] = carry + incl - tiles;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) {
+      prefix[p.batch] = carry;
+      for (int i = 0; i < P_NUM_BARS; ++i) {
+        const uint32_t count = (i == P_FULL0 || i == P_FULL1 || i == O_FREE || i == STAGE_FREE) ? 4u
+                               : (i == ITEM_FREE0 || i == ITEM_FREE1)                            ? 5u
+                                                                                                 : 1u;
+        mbar_init(bar(i), count);
+      }
+      *abort_flag = 0;
+      mbar_fence_init();
+      prefetch_tmap(&tmap_q);
+      prefetch_tmap(&tmap_k);
+      prefetch_tmap(&tmap_v);
+    }
+  }
+  if (warp == 5) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tmem_o = tmem + 128;
+
+  auto read_item = [&](int it) {
+    volatile int* s = slots + (it & 1) * 8;
+    Item x;
+    x.b = s[0]; x.h = s[1]; x.m0 = s[2]; x.q0 = s[3];
+    x.Lq = s[4]; x.k0 = s[5]; x.Lk = s[6]; x.n_kv = s[7];
+    return x;
+  };
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ producer lane
+    if (lane == 0) {
+      const int total_items = prefix[p.batch] * p.hq;
+      int T = 0;   // key tiles loaded so far in this block's life
+      int nq = 0;  // items with at least one key tile so far (Q_FULL phase)
+      for (int it = 0;; ++it) {
+        // next item: (query tile of a sequence, head); heads vary fastest so that the blocks
+        // working side by side share K/V tiles in L2
+        Item x;
+        while (true) {
+          x.n_kv = -1;
+          const unsigned idx = atomicAdd(&g_item_counter[counter_slot], 1u);
+          if (idx >= static_cast<unsigned>(total_items)) break;
+          const int pi = idx / p.hq;
+          x.h = idx - pi * p.hq;
+          int lo = 0, hi = p.batch;  // largest b with prefix[b] <= pi
+          while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (prefix[mid] <= pi) lo = mid; else hi = mid;
+          }
+          x.b = lo;
+          x.q0 = p.cu_q[lo];
+          x.Lq = p.cu_q[lo + 1] - x.q0;
+          x.k0 = p.cu_k[lo];
+          x.Lk = p.cu_k[lo + 1] - x.k0;
+          const int tiles = prefix[lo + 1] - prefix[lo];
+          x.m0 = (tiles - 1 - (pi - prefix[lo])) * BM;  // a sequence's long tiles first
+          const int kv_end = min(x.Lk, min(x.m0 + BM, x.Lq) + (x.Lk - x.Lq));
+          x.n_kv = kv_end > 0 ? (kv_end + BN - 1) / BN : 0;
+          if (x.n_kv > 0) break;
+          // No visible key for the whole tile (only possible when Lk < Lq, which the engine
+          // never produces): the rows are zero; written here, the other roles never see it.
+          for (int r = x.m0; r < min(x.m0 + BM, x.Lq); ++r) {
+            uint4* dst = reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(x.q0 + r) * p.out_stride + x.h * D);
+            for (int c = 0; c < 16; ++c) dst[c] = make_uint4(0, 0, 0, 0);
+          }
+        }
+        if (it >= 2 && !wait_or_abort(bar(ITEM_FREE0 + (it & 1)), ((it >> 1) - 1) & 1, abort_flag)) break;
+        volatile int* s = slots + (it & 1) * 8;
+        s[0] = x.b; s[1] = x.h; s[2] = x.m0; s[3] = x.q0;
+        s[4] = x.Lq; s[5] = x.k0; s[6] = x.Lk; s[7] = x.n_kv;
+        mbar_arrive(bar(ITEM_FULL0 + (it & 1)));
+        if (x.n_kv < 0) break;
+
+        const int kvh = x.h / p.g;
+        // Q buffer: free once the last S product of the previous item is complete
+        if (T > 0 && !wait_or_abort(bar(QK_DONE0 + ((T - 1) & 1)), ((T - 1) >> 1) & 1, abort_flag)) break;
+        mbar_expect_tx(bar(Q_FULL), Q_BYTES);
+        tma_load_3d(base + OFF_Q, &tmap_q, bar(Q_FULL), 0, x.h, x.q0 + x.m0);
+        tma_load_3d(base + OFF_Q + Q_SUB, &tmap_q, bar(Q_FULL), 64, x.h, x.q0 + x.m0);
+        ++nq;
+        const int32_t* bt_row = p.block_tables ? p.block_tables + x.b * p.bt_stride : nullptr;
+        bool ok = true;
+        for (int j = 0; j < x.n_kv; ++j) {
+          const int t = T + j, st = t & 1, use = t >> 1;
+          int row;
+          if (bt_row) {
+            int64_t blk = bt_row[(j * BN) / kBlockSize];
+            if (blk < 0 || blk >= p.num_blocks) {
+              atomicOr(p.status, NVLLM_STATUS_BAD_BLOCK);
+              blk = 0;
+            }
+            row = static_cast<int>(blk * kBlockSize + (j * BN) % kBlockSize);
+          } else {
+            row = x.k0 + j * BN;
+          }
+          if (use > 0 && !(ok = wait_or_abort(bar(QK_DONE0 + st), (use - 1) & 1, abort_flag))) break;
+          mbar_expect_tx(bar(K_FULL0 + st), KV_BYTES);
+          tma_load_3d(base + OFF_K + st * KV_BYTES, &tmap_k, bar(K_FULL0 + st), 0, kvh, row);
+          tma_load_3d(base + OFF_K + st * KV_BYTES + KV_SUB, &tmap_k, bar(K_FULL0 + st), 64, kvh, row);
+          if (use > 0 && !(ok = wait_or_abort(bar(PV_DONE0 + st), (use - 1) & 1, abort_flag))) break;
+          // the previous item's epilogue stages O through both V stages
+          if (j < 2 && it > 0 && !(ok = wait_or_abort(bar(STAGE_FREE), (it - 1) & 1, abort_flag))) break;
+          mbar_expect_tx(bar(V_FULL0 + st), KV_BYTES);
+          tma_load_3d(base + OFF_V + st * KV_BYTES, &tmap_v, bar(V_FULL0 + st), 0, kvh, row);
+          tma_load_3d(base + OFF_V + st * KV_BYTES + KV_SUB, &tmap_v, bar(V_FULL0 + st), 64, kvh, row);
+        }
+        if (!ok) break;
+        T += x.n_kv;
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc(BM, BN, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc(BM, D, 0, 1);
+      const uint64_t q_desc = umma_desc(base + OFF_Q, 16, 1024);
+      const uint64_t k_desc = umma_desc(base + OFF_K, 16, 1024);
+      const uint64_t v_desc = umma_desc(base + OFF_V, KV_SUB, 1024);
+      auto issue_qk = [&](int t) -> bool {
+        const int st = t & 1;
+        if (!wait_or_abort(bar(K_FULL0 + st), (t >> 1) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint64_t kd = k_desc + static_cast<uint64_t>(st * (KV_BYTES >> 4));
+        const uint32_t d_tmem = tmem + st * 64;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint64_t qoff = ((ks >> 2) * Q_SUB + (ks & 3) * 32) >> 4;
+          const uint64_t koff = ((ks >> 2) * KV_SUB + (ks & 3) * 32) >> 4;
+          umma_ss(d_tmem, q_desc + qoff, kd + koff, idesc_qk, ks > 0);
+        }
+        umma_commit(bar(QK_DONE0 + st));
+        return true;
+      };
+      int T = 0, nq = 0;
+      bool ok = true;
+      for (int it = 0; ok; ++it) {
+        if (!(ok = wait_or_abort(bar(ITEM_FULL0 + (it & 1)), (it >> 1) & 1, abort_flag))) break;
+        const Item x = read_item(it);
+        if (x.n_kv < 0) break;
+        {
+          if (!(ok = wait_or_abort(bar(Q_FULL), nq & 1, abort_flag))) break;
+          ++nq;
+          if (!(ok = issue_qk(T))) break;
+          for (int j = 0; j < x.n_kv; ++j) {
+            const int t = T + j, st = t & 1, ph = (t >> 1) & 1;
+            if (j + 1 < x.n_kv && !(ok = issue_qk(t + 1))) break;  // next S runs under this tile's softmax
+            if (!(ok = wait_or_abort(bar(V_FULL0 + st), ph, abort_flag))) break;
+            if (!(ok = wait_or_abort(bar(P_FULL0 + st), ph, abort_flag))) break;
+            // the first product of an item overwrites O: the previous item's O must have been read
+            if (j == 0 && it > 0 && !(ok = wait_or_abort(bar(O_FREE), (it - 1) & 1, abort_flag))) break;
+            tc_fence_after();
+            const uint64_t vd = v_desc + static_cast<uint64_t>(st * (KV_BYTES >> 4));
+            const uint32_t p_tmem = tmem + st * 64;
+#pragma unroll
+            for (int ks = 0; ks < BN / 16; ++ks)
+              umma_ts(tmem_o, p_tmem + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
+                      (j > 0 || ks > 0) ? 1u : 0u);
+            umma_commit(bar(PV_DONE0 + st));
+          }
+          if (!ok) break;
+          T += x.n_kv;
+        }
+        mbar_arrive(bar(ITEM_FREE0 + (it & 1)));
+      }
+      if (!ok) {  // make sure nothing is still running on TMEM before it is freed
+        umma_commit(bar(DRAIN));
+        (void)mbar_wait(bar(DRAIN), 0);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax rows
+    const int r = warp * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    unsigned char* stage = base_ptr + OFF_V;  // both V stages = one 32 KB O tile in bf16
+    int T = 0;
+    bool ok = true;
+    for (int it = 0; ok; ++it) {
+      if (!(ok = wait_or_abort(bar(ITEM_FULL0 + (it & 1)), (it >> 1) & 1, abort_flag))) break;
+      const Item x = read_item(it);
+      if (x.n_kv < 0) break;
+      const int qi = x.m0 + r, off = x.Lk - x.Lq;
+      float m_used = -INFINITY, l = 0.f;
+      for (int j = 0; j < x.n_kv; ++j) {
+        const int t = T + j, st = t & 1, ph = (t >> 1) & 1;
+        const uint32_t tmem_s = tmem + st * 64 + lane_addr;
+        if (!(ok = wait_or_abort(bar(QK_DONE0 + st), ph, abort_flag))) break;
+        tc_fence_after();
+        uint32_t s[64];
+        tmem_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        tmem_ld32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+        tmem_wait_ld();
+
+        const int j0 = j * BN;
+        if ((j0 + BN - 1 > x.m0 + off) || (j0 + BN > x.Lk)) {  // tile touches the diagonal or the end
+          const int limit = min(qi + off, x.Lk - 1) - j0;        // columns c <= limit are visible
+#pragma unroll
+          for (int c = 0; c < 64; ++c)
+            if (c > limit) s[c] = 0xff800000u;  // -inf
+        }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(s[c]));
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        const float m_new = fmaxf(m_used, mx * p.scale_log2e);
+        // lazy rescale: keep the old reference maximum unless it has been outgrown by 2^8
+        const bool grow = m_new > m_used + kRescaleThreshold;
+        if (__any_sync(0xffffffffu, grow)) {
+          float alpha = 1.f;
+          if (grow) {
+            alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
+            m_used = m_new;
+            l *= alpha;
+          }
+          if (j > 0) {  // O holds tiles 0..j-1 of this item once the previous P V product has finished
+            if (!(ok = wait_or_abort(bar(PV_DONE0 + ((t - 1) & 1)), ((t - 1) >> 1) & 1, abort_flag))) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t o[32];
+              tmem_ld32(tmem_o + lane_addr + c * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+              tmem_st32(tmem_o + lane_addr + c * 32, o);
+            }
+          }
+        }
+        const float msub = (m_used == -INFINITY) ? 0.f : m_used;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {  // P is packed in place: s[c] <- (p[2c], p[2c+1])
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s[2 * c]), p.scale_log2e, -msub));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s[2 * c + 1]), p.scale_log2e, -msub));
+          sum4[c & 3] += p0 + p1;
+          s[c] = pack_bf16x2(p0, p1);
+        }
+        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        if (j0 + BN > x.Lk) {
+          // Last tile of the sequence: V rows past the end hold whatever the cache block (or the
+          // next sequence) has there.  Their P is 0, but 0 x NaN would still poison O, so the
+          // rows are cleared in shared memory before the product is issued.
+          if (!(ok = wait_or_abort(bar(V_FULL0 + st), ph, abort_flag))) break;
+          const int first = x.Lk - j0;  // rows [first, 64) are dead
+          unsigned char* vt = base_ptr + OFF_V + st * KV_BYTES;
+          for (int i = r; i < (BN - first) * 16; i += 128) {
+            const int row = first + (i >> 4), piece = i & 15;
+            *reinterpret_cast<uint4*>(vt + (piece >> 3) * KV_SUB + row * 128 + (piece & 7) * 16) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async();
+        }
+        tmem_st32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(P_FULL0 + st));
+      }
+      if (!ok) break;
+      T += x.n_kv;
+
+      // epilogue: O / l -> bf16, staged through the V ring, stored as whole rows
+      if (!(ok = wait_or_abort(bar(PV_DONE0 + ((T - 1) & 1)), ((T - 1) >> 1) & 1, abort_flag))) break;
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        tmem_ld32(tmem_o + lane_addr + c * 32, o);
+        tmem_wait_ld();
+        if (c == 3) {  // O is in registers: the next item's first product may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(O_FREE));
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          uint4 v;
+          v.x = pack_bf16x2(__uint_as_float(o[8 * k]) * inv, __uint_as_float(o[8 * k + 1]) * inv);
+          v.y = pack_bf16x2(__uint_as_float(o[8 * k + 2]) * inv, __uint_as_float(o[8 * k + 3]) * inv);
+          v.z = pack_bf16x2(__uint_as_float(o[8 * k + 4]) * inv, __uint_as_float(o[8 * k + 5]) * inv);
+          v.w = pack_bf16x2(__uint_as_float(o[8 * k + 6]) * inv, __uint_as_float(o[8 * k + 7]) * inv);
+          const int cc = c * 4 + k;  // 16-byte piece of the row
+          *reinterpret_cast<uint4*>(stage + r * 256 + ((cc ^ (r & 15)) << 4)) = v;
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four softmax warps only
+      __nv_bfloat16* out_tile = p.out + static_cast<int64_t>(x.q0 + x.m0) * p.out_stride + x.h * D;
+      const int rows_valid = min(BM, x.Lq - x.m0);
+#pragma unroll 4
+      for (int idx = r; idx < BM * 16; idx += 128) {
+        const int row = idx >> 4, cc = idx & 15;
+        if (row < rows_valid)
+          *reinterpret_cast<uint4*>(out_tile + static_cast<int64_t>(row) * p.out_stride + cc * 8) =
+              *reinterpret_cast<const uint4*>(stage + row * 256 + ((cc ^ (row & 15)) << 4));
+      }
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar(STAGE_FREE));
+        mbar_arrive(bar(ITEM_FREE0 + (it & 1)));
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0) {
+    if (*abort_flag) atomicOr(p.status, NVLLM_STATUS_TIMEOUT);
+    // the last block to leave re-arms this launch slot's counters
+    if (atomicAdd(&g_done_counter[counter_slot], 1u) == gridDim.x - 1) {
+      g_item_counter[counter_slot] = 0;
+      g_done_counter[counter_slot] = 0;
+      __threadfence();
+    }
+  }
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------
+
+int launch_prefill_tcp(const PrefillParams& p, int64_t total_q, int64_t total_k, cudaStream_t stream) {
+  static bool attr_done[64] = {false};
+  static int num_sms[64] = {0};
+  static std::atomic<unsigned> launch_seq{0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return fail(NVLLM_E_NO_DEVICE, "prefill: device index %d out of range", dev);
+  if (!attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_tcp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tcp::SMEM);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return fail(NVLLM_E_CUDA, "prefill (persistent): set-up failed: %s", cudaGetErrorString(e));
+    attr_done[dev] = true;
+  }
+  CUtensorMap mq, mk, mv;
+  if (!make_tmap_3d(&mq, p.q, tc::D, p.hq, total_q, tc::D, p.q_stride, tc::BM)) return NVLLM_E_CUDA;
+  if (p.block_tables) {
+    const uint64_t slots = static_cast<uint64_t>(p.num_blocks) * kBlockSize;
+    const uint64_t row = static_cast<uint64_t>(p.hkv) * tc::D;
+    if (!make_tmap_3d(&mk, p.k, tc::D, p.hkv, slots, tc::D, row, tc::BN)) return NVLLM_E_CUDA;
+    if (!make_tmap_3d(&mv, p.v, tc::D, p.hkv, slots, tc::D, row, tc::BN)) return NVLLM_E_CUDA;
+  } else {
+    if (!make_tmap_3d(&mk, p.k, tc::D, p.hkv, total_k, tc::D, p.k_stride, tc::BN)) return NVLLM_E_CUDA;
+    if (!make_tmap_3d(&mv, p.v, tc::D, p.hkv, total_k, tc::D, p.v_stride, tc::BN)) return NVLLM_E_CUDA;
+  }
+  // an upper bound of the work items known to the host: no more blocks than that
+  const int64_t max_items = static_cast<int64_t>((p.max_seqlen_q + tc::BM - 1) / tc::BM) * p.hq * p.batch;
+  int grid = 2 * num_sms[dev];
+  if (max_items < grid) grid = static_cast<int>(max_items);
+  const int slot = static_cast<int>(launch_seq.fetch_add(1) % tcp::NUM_SLOTS);
+  prefill_tcp_kernel<<<grid, tc::NTHREADS, tcp::SMEM, stream>>>(p, mq, mk, mv, slot);
+  count_launch();
+  return check_launch("prefill (tcgen05, persistent) launch");
+}
+
+}  // namespace nvllm
