@@ -175,6 +175,14 @@ NVLLM_API int nvllm_prefill_varlen(const void* q, int64_t q_row_stride,
  * A diagnostic for new driver / toolkit versions.  No counterpart in the reference. */
 NVLLM_API int nvllm_selftest_umma(const void* a, const void* b, float* out_ss, float* out_ts, void* stream);
 
+/* Failure-detection check that faults nothing: a one-block kernel waits on a barrier that
+ * nothing signals.  The wait gives up after about one second, a second waiter leaves through
+ * the block's abort flag, NVLLM_STATUS_TIMEOUT is recorded in the status word, and the block
+ * frees its tensor memory and ends normally (the context stays usable).  device_result (two
+ * int32 in device memory) receives 0/0: both waits reported failure.  No counterpart in the
+ * reference. */
+NVLLM_API int nvllm_selftest_wait_expiry(int32_t* device_result, void* stream);
+
 /* Message for the last negative return value on this thread ("" if none).
  * No counterpart in the reference (it raises Python exceptions). */
 NVLLM_API const char* nvllm_last_error(void);

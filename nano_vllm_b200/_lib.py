@@ -31,6 +31,7 @@ SIGNATURES = {
                                        c_int32, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int32,
                                        c_int32, c_int32, c_int32, c_int32, c_int32, c_float, c_int64, c_void_p]),
     "nvllm_selftest_umma": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nvllm_selftest_wait_expiry": (c_int32, [c_void_p, c_void_p]),
     "nvllm_last_error": (c_char_p, []),
     "nvllm_read_status": (c_int32, [POINTER(c_int32)]),
     "nvllm_abi_version": (c_int32, []),

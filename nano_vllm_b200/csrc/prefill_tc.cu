@@ -452,6 +452,36 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   }
 }
 
+// ---- bounded-wait check ---------------------------------------------------------------------
+// One block allocates TMEM, then a thread waits on an mbarrier that nothing ever arrives at.
+// The wait must run out (about a second), set the abort flag that the other roles poll, record
+// NVLLM_STATUS_TIMEOUT, and the block must still free its TMEM and end normally.
+__global__ void __launch_bounds__(64, 1) wait_expiry_selftest_kernel(int* __restrict__ status, int* __restrict__ result) {
+  __shared__ __align__(8) uint64_t bars[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    mbar_init(smem_u32(&bars[0]), 1);
+    mbar_init(smem_u32(&bars[1]), 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_slot), 64);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  bool ok = true;
+  if (tid == 0) ok = wait_or_abort(smem_u32(&bars[0]), 0, abort_flag);   // runs out on the clock
+  if (tid == 32) ok = wait_or_abort(smem_u32(&bars[1]), 0, abort_flag);  // leaves early through the abort flag
+  if (tid == 0) result[0] = ok ? 1 : 0;
+  if (tid == 32) result[1] = ok ? 1 : 0;
+  __syncthreads();
+  if (tid == 0 && *abort_flag) atomicOr(status, NVLLM_STATUS_TIMEOUT);
+  if (warp == 1) tmem_dealloc(tmem_slot, 64);
+}
+
 // ---- host side ---------------------------------------------------------------------------
 
 template <class K>
@@ -502,6 +532,16 @@ extern "C" __attribute__((visibility("default"))) int nvllm_debug_phase_clocks(l
   return cudaMemcpyFromSymbol(host_out, nvllm::g_phase_clocks, sizeof(long long) * 64 * 12) == cudaSuccess ? 0 : -5;
 }
 #endif
+
+extern "C" int nvllm_selftest_wait_expiry(int32_t* device_result, void* stream) {
+  using namespace nvllm;
+  if (!device_result) return fail(NVLLM_E_NULL, "selftest_wait_expiry: device_result is NULL");
+  int* status = status_word();
+  if (!status) return fail(NVLLM_E_NO_DEVICE, "selftest_wait_expiry: no CUDA device is usable");
+  wait_expiry_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(status, device_result);
+  count_launch();
+  return check_launch("selftest_wait_expiry launch");
+}
 
 extern "C" int nvllm_selftest_umma(const void* a, const void* b, float* out_ss, float* out_ts, void* stream) {
   using namespace nvllm;
