@@ -57,7 +57,7 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=256, help="sequences in the decode batch")
     ap.add_argument("--no-secondary", action="store_true", help="skip the store/prefill/long-context extras")
-    ap.add_argument("--kernel", default=None, choices=["prefill", "prefill_long", "store", "decode_long"],
+    ap.add_argument("--kernel", default=None, choices=["prefill", "prefill_long", "prefill_d64", "store", "decode_long"],
                     help="time only this secondary kernel on one GPU and print its line (profiling aid)")
     return ap.parse_args()
 
@@ -400,6 +400,19 @@ def secondary(dev, hbm_peak_gbs, only=None):
         ms = med(lambda: A.prefill_varlen(pl.q, pl.k, pl.v, pl.cu_seqlens_q, pl.cu_seqlens_k, 4096, 4096, pl.scale, out=o))
         res["prefill_4x4096_packed"] = tf_line(ms, fl)
         del pl, o
+    if only in (None, "prefill_d64"):
+        # config-2 lengths in Qwen2-0.5B geometry (14 q / 2 kv heads, head_dim 64)
+        pd = W.make_prefill_case(2, 64, 100, 1024, device=dev, **W.QWEN2_05B)
+        A.store_kvcache(pd.k, pd.v, pd.k_cache, pd.v_cache, pd.slot_mapping)
+        lq = (pd.cu_seqlens_q[1:] - pd.cu_seqlens_q[:-1]).tolist()
+        lk = (pd.cu_seqlens_k[1:] - pd.cu_seqlens_k[:-1]).tolist()
+        fl = W.prefill_flops(lq, lk, 14, 64)
+        o = torch.empty_like(pd.q)
+        ms = med(lambda: A.prefill_varlen(pd.q, pd.k_cache, pd.v_cache, pd.cu_seqlens_q, pd.cu_seqlens_k,
+                                          pd.max_seqlen_q, pd.max_seqlen_k, pd.scale,
+                                          block_tables=pd.block_tables, out=o))
+        res["prefill_cfg2_lengths_qwen2_d64"] = tf_line(ms, fl)
+        del pd, o
     if only in (None, "decode_long"):
         c5 = W.cfg5_decode(1, dev, batch=256)
         B, Hq, Hkv, D = c5.geometry

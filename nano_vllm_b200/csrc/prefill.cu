@@ -64,16 +64,18 @@ extern "C" int nvllm_prefill_varlen(const void* q, int64_t q_row_stride, const v
   p.d = head_dim;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.num_blocks = num_blocks;
-  // NVLLM_PREFILL_IMPL = mma | tc | tcp picks a kernel by hand (measurement aid); the default is
-  // the persistent tcgen05 kernel for head_dim 128 and the mma.sync kernel otherwise.
-  static const char impl = [] {
-    const char* s = std::getenv("NVLLM_PREFILL_IMPL");
-    if (!s || !*s) return 'a';
-    return (s[0] == 'm') ? 'm' : (s[0] == 't' && s[1] == 'c' && s[2] == 'p') ? 'p' : (s[0] == 't') ? 't' : 'a';
-  }();
-  if (head_dim == 128 && impl != 'm' && (block_tables || total_k > 0)) {
-    if (impl != 't' && batch <= 1024) return launch_prefill_tcp(p, total_q, total_k, static_cast<cudaStream_t>(stream));
-    return launch_prefill_tc(p, total_q, total_k, static_cast<cudaStream_t>(stream));
+  // NVLLM_PREFILL_IMPL = mma | tc | tcp picks a kernel by hand (measurement and test aid, read on
+  // every call); by default the persistent tcgen05 kernel runs whenever it can.
+  char impl = 'a';
+  if (const char* s = std::getenv("NVLLM_PREFILL_IMPL")) {
+    if (s[0] == 'm') impl = 'm';
+    else if (s[0] == 't' && s[1] == 'c' && s[2] == 'p') impl = 'p';
+    else if (s[0] == 't') impl = 't';
   }
+  const bool has_rows = block_tables || total_k > 0;
+  if (impl != 'm' && impl != 't' && has_rows && batch <= 1024)
+    return launch_prefill_tcp(p, total_q, total_k, static_cast<cudaStream_t>(stream));
+  if (impl != 'm' && head_dim == 128 && has_rows)
+    return launch_prefill_tc(p, total_q, total_k, static_cast<cudaStream_t>(stream));
   return launch_prefill_mma(p, static_cast<cudaStream_t>(stream));
 }

@@ -33,11 +33,25 @@ constexpr int MAX_BATCH = 1024;  // prefix array of query tiles per sequence liv
 enum PBar {
   ITEM_FULL0 = tc::NUM_BARS, ITEM_FULL1, ITEM_FREE0, ITEM_FREE1, O_FREE, STAGE_FREE, P_NUM_BARS
 };
-constexpr int OFF_CTRL = OFF_BAR;                 // barriers (8 B each)
-constexpr int OFF_SLOTS = OFF_CTRL + 256;         // two item descriptors of 8 ints
-constexpr int OFF_MISC = OFF_SLOTS + 64;          // tmem address, abort flag
-constexpr int OFF_PREFIX = OFF_MISC + 64;         // (MAX_BATCH + 1) ints
-constexpr int SMEM = OFF_PREFIX + (MAX_BATCH + 1) * 4 + 60 + 1024;
+// Shared-memory layout and tile sizes for one head_dim (64 or 128).  A tile row is split into
+// 64-element (128-byte) sub-tiles, the unit of the 128-byte swizzle.
+template <int D_>
+struct Geo {
+  static constexpr int D = D_;
+  static constexpr int NSUB = D / 64;               // sub-tiles per tile row
+  static constexpr int Q_SUB = BM * 128, Q_BYTES = NSUB * Q_SUB;
+  static constexpr int KV_SUB = BN * 128, KV_BYTES = NSUB * KV_SUB;
+  static constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + KST * KV_BYTES;
+  static constexpr int OFF_CTRL = OFF_V + KST * KV_BYTES;  // barriers (8 B each)
+  static constexpr int OFF_SLOTS = OFF_CTRL + 256;         // two item descriptors of 8 ints
+  static constexpr int OFF_MISC = OFF_SLOTS + 64;          // tmem address, abort flag
+  static constexpr int OFF_PREFIX = OFF_MISC + 64;         // (MAX_BATCH + 1) ints
+  static constexpr int SMEM = OFF_PREFIX + (MAX_BATCH + 1) * 4 + 60 + 1024;
+  static constexpr int OCH = D / 32;      // 32-column chunks of O
+  static constexpr int ROWB = D * 2;      // bytes of one output row
+  static constexpr int PIECES = D / 8;    // 16-byte pieces of one row
+  static_assert(BM * ROWB == KST * KV_BYTES, "the epilogue stages O through the whole V ring");
+};
 constexpr int NUM_SLOTS = 64;                     // launches that may be in flight at once
 static_assert(P_NUM_BARS * 8 <= 256, "barrier area");
 }  // namespace tcp
@@ -50,11 +64,17 @@ struct Item {
   int b, h, m0, q0, Lq, k0, Lk, n_kv;  // n_kv < 0: no more work
 };
 
+template <int D>
 __global__ void __launch_bounds__(tc::NTHREADS, 2)
 prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                    const int counter_slot) {
   using namespace tcp;
+  using G = Geo<D>;
+  constexpr int Q_BYTES = G::Q_BYTES, Q_SUB = G::Q_SUB, KV_BYTES = G::KV_BYTES, KV_SUB = G::KV_SUB;
+  constexpr int OFF_Q = G::OFF_Q, OFF_K = G::OFF_K, OFF_V = G::OFF_V, OFF_CTRL = G::OFF_CTRL;
+  constexpr int OFF_SLOTS = G::OFF_SLOTS, OFF_MISC = G::OFF_MISC, OFF_PREFIX = G::OFF_PREFIX;
+  constexpr int OCH = G::OCH, ROWB = G::ROWB, PIECES = G::PIECES;
   extern __shared__ unsigned char smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
@@ -148,7 +168,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
           // never produces): the rows are zero; written here, the other roles never see it.
           for (int r = x.m0; r < min(x.m0 + BM, x.Lq); ++r) {
             uint4* dst = reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(x.q0 + r) * p.out_stride + x.h * D);
-            for (int c = 0; c < 16; ++c) dst[c] = make_uint4(0, 0, 0, 0);
+            for (int c = 0; c < PIECES; ++c) dst[c] = make_uint4(0, 0, 0, 0);
           }
         }
         if (it >= 2 && !wait_or_abort(bar(ITEM_FREE0 + (it & 1)), ((it >> 1) - 1) & 1, abort_flag)) break;
@@ -163,7 +183,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
         if (T > 0 && !wait_or_abort(bar(QK_DONE0 + ((T - 1) & 1)), ((T - 1) >> 1) & 1, abort_flag)) break;
         mbar_expect_tx(bar(Q_FULL), Q_BYTES);
         tma_load_3d(base + OFF_Q, &tmap_q, bar(Q_FULL), 0, x.h, x.q0 + x.m0);
-        tma_load_3d(base + OFF_Q + Q_SUB, &tmap_q, bar(Q_FULL), 64, x.h, x.q0 + x.m0);
+        if constexpr (G::NSUB == 2) tma_load_3d(base + OFF_Q + Q_SUB, &tmap_q, bar(Q_FULL), 64, x.h, x.q0 + x.m0);
         ++nq;
         const int32_t* bt_row = p.block_tables ? p.block_tables + x.b * p.bt_stride : nullptr;
         bool ok = true;
@@ -183,13 +203,13 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
           if (use > 0 && !(ok = wait_or_abort(bar(QK_DONE0 + st), (use - 1) & 1, abort_flag))) break;
           mbar_expect_tx(bar(K_FULL0 + st), KV_BYTES);
           tma_load_3d(base + OFF_K + st * KV_BYTES, &tmap_k, bar(K_FULL0 + st), 0, kvh, row);
-          tma_load_3d(base + OFF_K + st * KV_BYTES + KV_SUB, &tmap_k, bar(K_FULL0 + st), 64, kvh, row);
+          if constexpr (G::NSUB == 2) tma_load_3d(base + OFF_K + st * KV_BYTES + KV_SUB, &tmap_k, bar(K_FULL0 + st), 64, kvh, row);
           if (use > 0 && !(ok = wait_or_abort(bar(PV_DONE0 + st), (use - 1) & 1, abort_flag))) break;
           // the previous item's epilogue stages O through both V stages
           if (j < 2 && it > 0 && !(ok = wait_or_abort(bar(STAGE_FREE), (it - 1) & 1, abort_flag))) break;
           mbar_expect_tx(bar(V_FULL0 + st), KV_BYTES);
           tma_load_3d(base + OFF_V + st * KV_BYTES, &tmap_v, bar(V_FULL0 + st), 0, kvh, row);
-          tma_load_3d(base + OFF_V + st * KV_BYTES + KV_SUB, &tmap_v, bar(V_FULL0 + st), 64, kvh, row);
+          if constexpr (G::NSUB == 2) tma_load_3d(base + OFF_V + st * KV_BYTES + KV_SUB, &tmap_v, bar(V_FULL0 + st), 64, kvh, row);
         }
         if (!ok) break;
         T += x.n_kv;
@@ -302,7 +322,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
             if (!(ok = wait_or_abort(bar(PV_DONE0 + ((t - 1) & 1)), ((t - 1) >> 1) & 1, abort_flag))) break;
             tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < OCH; ++c) {
               uint32_t o[32];
               tmem_ld32(tmem_o + lane_addr + c * 32, o);
               tmem_wait_ld();
@@ -329,8 +349,8 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
           if (!(ok = wait_or_abort(bar(V_FULL0 + st), ph, abort_flag))) break;
           const int first = x.Lk - j0;  // rows [first, 64) are dead
           unsigned char* vt = base_ptr + OFF_V + st * KV_BYTES;
-          for (int i = r; i < (BN - first) * 16; i += 128) {
-            const int row = first + (i >> 4), piece = i & 15;
+          for (int i = r; i < (BN - first) * PIECES; i += 128) {
+            const int row = first + i / PIECES, piece = i % PIECES;
             *reinterpret_cast<uint4*>(vt + (piece >> 3) * KV_SUB + row * 128 + (piece & 7) * 16) = make_uint4(0, 0, 0, 0);
           }
           fence_proxy_async();
@@ -349,11 +369,11 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < OCH; ++c) {
         uint32_t o[32];
         tmem_ld32(tmem_o + lane_addr + c * 32, o);
         tmem_wait_ld();
-        if (c == 3) {  // O is in registers: the next item's first product may overwrite it
+        if (c == OCH - 1) {  // O is in registers: the next item's first product may overwrite it
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(O_FREE));
@@ -366,18 +386,18 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
           v.z = pack_bf16x2(__uint_as_float(o[8 * k + 4]) * inv, __uint_as_float(o[8 * k + 5]) * inv);
           v.w = pack_bf16x2(__uint_as_float(o[8 * k + 6]) * inv, __uint_as_float(o[8 * k + 7]) * inv);
           const int cc = c * 4 + k;  // 16-byte piece of the row
-          *reinterpret_cast<uint4*>(stage + r * 256 + ((cc ^ (r & 15)) << 4)) = v;
+          *reinterpret_cast<uint4*>(stage + r * ROWB + ((cc ^ (r & (PIECES - 1))) << 4)) = v;
         }
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");  // the four softmax warps only
       __nv_bfloat16* out_tile = p.out + static_cast<int64_t>(x.q0 + x.m0) * p.out_stride + x.h * D;
       const int rows_valid = min(BM, x.Lq - x.m0);
 #pragma unroll 4
-      for (int idx = r; idx < BM * 16; idx += 128) {
-        const int row = idx >> 4, cc = idx & 15;
+      for (int idx = r; idx < BM * PIECES; idx += 128) {
+        const int row = idx / PIECES, cc = idx % PIECES;
         if (row < rows_valid)
           *reinterpret_cast<uint4*>(out_tile + static_cast<int64_t>(row) * p.out_stride + cc * 8) =
-              *reinterpret_cast<const uint4*>(stage + row * 256 + ((cc ^ (row & 15)) << 4));
+              *reinterpret_cast<const uint4*>(stage + row * ROWB + ((cc ^ (row & (PIECES - 1))) << 4));
       }
       __syncwarp();
       if (lane == 0) {
@@ -406,7 +426,9 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
 
 // ---- host side ---------------------------------------------------------------------------
 
-int launch_prefill_tcp(const PrefillParams& p, int64_t total_q, int64_t total_k, cudaStream_t stream) {
+template <int D>
+static int launch_prefill_tcp_t(const PrefillParams& p, int64_t total_q, int64_t total_k, cudaStream_t stream) {
+  using G = tcp::Geo<D>;
   static bool attr_done[64] = {false};
   static int num_sms[64] = {0};
   static std::atomic<unsigned> launch_seq{0};
@@ -414,30 +436,36 @@ int launch_prefill_tcp(const PrefillParams& p, int64_t total_q, int64_t total_k,
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return fail(NVLLM_E_NO_DEVICE, "prefill: device index %d out of range", dev);
   if (!attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_tcp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tcp::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(prefill_tcp_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return fail(NVLLM_E_CUDA, "prefill (persistent): set-up failed: %s", cudaGetErrorString(e));
     attr_done[dev] = true;
   }
   CUtensorMap mq, mk, mv;
-  if (!make_tmap_3d(&mq, p.q, tc::D, p.hq, total_q, tc::D, p.q_stride, tc::BM)) return NVLLM_E_CUDA;
+  if (!make_tmap_3d(&mq, p.q, D, p.hq, total_q, D, p.q_stride, tc::BM)) return NVLLM_E_CUDA;
   if (p.block_tables) {
     const uint64_t slots = static_cast<uint64_t>(p.num_blocks) * kBlockSize;
-    const uint64_t row = static_cast<uint64_t>(p.hkv) * tc::D;
-    if (!make_tmap_3d(&mk, p.k, tc::D, p.hkv, slots, tc::D, row, tc::BN)) return NVLLM_E_CUDA;
-    if (!make_tmap_3d(&mv, p.v, tc::D, p.hkv, slots, tc::D, row, tc::BN)) return NVLLM_E_CUDA;
+    const uint64_t row = static_cast<uint64_t>(p.hkv) * D;
+    if (!make_tmap_3d(&mk, p.k, D, p.hkv, slots, D, row, tc::BN)) return NVLLM_E_CUDA;
+    if (!make_tmap_3d(&mv, p.v, D, p.hkv, slots, D, row, tc::BN)) return NVLLM_E_CUDA;
   } else {
-    if (!make_tmap_3d(&mk, p.k, tc::D, p.hkv, total_k, tc::D, p.k_stride, tc::BN)) return NVLLM_E_CUDA;
-    if (!make_tmap_3d(&mv, p.v, tc::D, p.hkv, total_k, tc::D, p.v_stride, tc::BN)) return NVLLM_E_CUDA;
+    if (!make_tmap_3d(&mk, p.k, D, p.hkv, total_k, D, p.k_stride, tc::BN)) return NVLLM_E_CUDA;
+    if (!make_tmap_3d(&mv, p.v, D, p.hkv, total_k, D, p.v_stride, tc::BN)) return NVLLM_E_CUDA;
   }
   // an upper bound of the work items known to the host: no more blocks than that
   const int64_t max_items = static_cast<int64_t>((p.max_seqlen_q + tc::BM - 1) / tc::BM) * p.hq * p.batch;
   int grid = 2 * num_sms[dev];
   if (max_items < grid) grid = static_cast<int>(max_items);
-  const int slot = static_cast<int>(launch_seq.fetch_add(1) % tcp::NUM_SLOTS);
-  prefill_tcp_kernel<<<grid, tc::NTHREADS, tcp::SMEM, stream>>>(p, mq, mk, mv, slot);
+  // the two head_dim instantiations share the counter array: give each its own half
+  const int slot = static_cast<int>(launch_seq.fetch_add(1) % (tcp::NUM_SLOTS / 2)) + (D == 64 ? tcp::NUM_SLOTS / 2 : 0);
+  prefill_tcp_kernel<D><<<grid, tc::NTHREADS, G::SMEM, stream>>>(p, mq, mk, mv, slot);
   count_launch();
   return check_launch("prefill (tcgen05, persistent) launch");
+}
+
+int launch_prefill_tcp(const PrefillParams& p, int64_t total_q, int64_t total_k, cudaStream_t stream) {
+  if (p.d == 128) return launch_prefill_tcp_t<128>(p, total_q, total_k, stream);
+  return launch_prefill_tcp_t<64>(p, total_q, total_k, stream);
 }
 
 }  // namespace nvllm

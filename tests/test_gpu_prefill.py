@@ -83,3 +83,22 @@ def test_stale_cache_rows_past_the_sequence_cannot_leak(cuda, d):
     case.k_cache[:] = float("nan")
     case.v_cache[:] = float("inf")
     _check(cuda, case, f"stale d{d}")
+
+
+@pytest.mark.parametrize("impl,d", [("mma", 64), ("mma", 128), ("tc", 128), ("tcp", 64), ("tcp", 128)])
+def test_every_prefill_kernel_on_the_same_case(cuda, monkeypatch, impl, d):
+    """NVLLM_PREFILL_IMPL selects the warp-level kernel (mma), the one-block-per-tile tcgen05
+    kernel (tc, head_dim 128 only) or the persistent tcgen05 kernel (tcp); all must agree with
+    the oracle on packed and on prefix-cached inputs."""
+    monkeypatch.setenv("NVLLM_PREFILL_IMPL", impl)
+    case = W.make_prefill_case(26, 7, 1, 1, 8, 2, d, lengths=[1, 130, 1024, 1024, 513, 700, 64],
+                               shared_blocks=[0, 0, 0, 3, 0, 2, 0])
+    _check(cuda, case, f"{impl} d{d} prefix")
+    case = W.make_prefill_case(27, 5, 1, 1, 8, 8, d, share_every=0, lengths=[257, 2, 900, 128, 64])
+    _check(cuda, case, f"{impl} d{d} packed")
+
+
+def test_many_sequences_through_the_persistent_kernel(cuda):
+    """More work items than resident blocks, and more sequences than one warp scans at once."""
+    case = W.make_prefill_case(28, 150, 1, 300, 4, 2, 128, share_every=0)
+    _check(cuda, case, "150 sequences")
