@@ -306,7 +306,12 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
         }
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 64; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(s[c]));
+        for (int c = 0; c < 64; c += 8) {
+          mx4[0] = fmax3(mx4[0], __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
+          mx4[1] = fmax3(mx4[1], __uint_as_float(s[c + 2]), __uint_as_float(s[c + 3]));
+          mx4[2] = fmax3(mx4[2], __uint_as_float(s[c + 4]), __uint_as_float(s[c + 5]));
+          mx4[3] = fmax3(mx4[3], __uint_as_float(s[c + 6]), __uint_as_float(s[c + 7]));
+        }
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         const float m_new = fmaxf(m_used, mx * p.scale_log2e);
         // lazy rescale: keep the old reference maximum unless it has been outgrown by 2^8
@@ -333,15 +338,23 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
           }
         }
         const float msub = (m_used == -INFINITY) ? 0.f : m_used;
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        // p = 2^(s * scale - m): the multiply-subtract and the row sum run two lanes at a time
+        const uint64_t scale2 = pack2(p.scale_log2e, p.scale_log2e), nmsub2 = pack2(-msub, -msub);
+        uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
         for (int c = 0; c < 32; ++c) {  // P is packed in place: s[c] <- (p[2c], p[2c+1])
-          const float p0 = fast_exp2(fmaf(__uint_as_float(s[2 * c]), p.scale_log2e, -msub));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(s[2 * c + 1]), p.scale_log2e, -msub));
-          sum4[c & 3] += p0 + p1;
+          float a0, a1;
+          unpack2(fma2(pack2(__uint_as_float(s[2 * c]), __uint_as_float(s[2 * c + 1])), scale2, nmsub2), a0, a1);
+          const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
+          sum2[c & 1] = add2(sum2[c & 1], pack2(p0, p1));
           s[c] = pack_bf16x2(p0, p1);
         }
-        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        {
+          float t0, t1, t2, t3;
+          unpack2(sum2[0], t0, t1);
+          unpack2(sum2[1], t2, t3);
+          l += (t0 + t1) + (t2 + t3);
+        }
         if (j0 + BN > x.Lk) {
           // Last tile of the sequence: V rows past the end hold whatever the cache block (or the
           // next sequence) has there.  Their P is 0, but 0 x NaN would still poison O, so the
