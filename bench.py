@@ -57,8 +57,11 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=256, help="sequences in the decode batch")
     ap.add_argument("--no-secondary", action="store_true", help="skip the store/prefill/long-context extras")
-    ap.add_argument("--kernel", default=None, choices=["prefill", "prefill_long", "prefill_d64", "store", "decode_long"],
+    ap.add_argument("--kernel", default=None, choices=["prefill", "prefill_long", "prefill_d64", "store", "decode", "decode_long"],
                     help="time only this secondary kernel on one GPU and print its line (profiling aid)")
+    ap.add_argument("--with-flash-attn", action="store_true",
+                    help="with --kernel: also time the library kernels the reference calls (flash-attn, Triton "
+                         "store) on the same inputs, if they are importable")
     return ap.parse_args()
 
 
@@ -338,7 +341,7 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def secondary(dev, hbm_peak_gbs, only=None):
+def secondary(dev, hbm_peak_gbs, only=None, compare=False):
     """Other kernels of the path, 1 GPU, device-timed (median of 20 after 3 warm-ups, L2
     flushed between iterations)."""
     import torch
@@ -371,6 +374,12 @@ def secondary(dev, hbm_peak_gbs, only=None):
             d["frac_of_bf16_peak"] = round(fl / ms / 1e9 / tf_peak, 3)
         return d
 
+    fa = None
+    if compare:
+        try:
+            import flash_attn as fa
+        except Exception:
+            fa = None
     res = {}
     if only in (None, "store", "prefill"):
         pc = W.cfg2_prefill(dev)
@@ -390,6 +399,13 @@ def secondary(dev, hbm_peak_gbs, only=None):
                                               pc.max_seqlen_q, pc.max_seqlen_k, pc.scale,
                                               block_tables=pc.block_tables, out=o))
             res["prefill_cfg2_paged"] = tf_line(ms, fl)
+            if fa:
+                bt = pc.block_tables.clamp(min=0)
+                ms = med(lambda: fa.flash_attn_varlen_func(pc.q, pc.k_cache, pc.v_cache, max_seqlen_q=pc.max_seqlen_q,
+                                                           cu_seqlens_q=pc.cu_seqlens_q, max_seqlen_k=pc.max_seqlen_k,
+                                                           cu_seqlens_k=pc.cu_seqlens_k, softmax_scale=pc.scale,
+                                                           causal=True, block_table=bt))
+                res["flash_attn_prefill_cfg2_paged"] = tf_line(ms, fl)
             del o
         del pc
     if only in (None, "prefill_long"):
@@ -399,6 +415,11 @@ def secondary(dev, hbm_peak_gbs, only=None):
         o = torch.empty_like(pl.q)
         ms = med(lambda: A.prefill_varlen(pl.q, pl.k, pl.v, pl.cu_seqlens_q, pl.cu_seqlens_k, 4096, 4096, pl.scale, out=o))
         res["prefill_4x4096_packed"] = tf_line(ms, fl)
+        if fa:
+            ms = med(lambda: fa.flash_attn_varlen_func(pl.q, pl.k, pl.v, max_seqlen_q=4096, cu_seqlens_q=pl.cu_seqlens_q,
+                                                       max_seqlen_k=4096, cu_seqlens_k=pl.cu_seqlens_k,
+                                                       softmax_scale=pl.scale, causal=True))
+            res["flash_attn_prefill_4x4096_packed"] = tf_line(ms, fl)
         del pl, o
     if only in (None, "prefill_d64"):
         # config-2 lengths in Qwen2-0.5B geometry (14 q / 2 kv heads, head_dim 64)
@@ -413,6 +434,23 @@ def secondary(dev, hbm_peak_gbs, only=None):
                                           block_tables=pd.block_tables, out=o))
         res["prefill_cfg2_lengths_qwen2_d64"] = tf_line(ms, fl)
         del pd, o
+    if only == "decode":
+        # the headline workload (config 4, batch 256), kernel only, next to the library kernel
+        c4 = W.cfg4_decode(1, 0, dev)
+        B, Hq, Hkv, D = c4.geometry
+        nb = W.decode_bytes(c4.context_lens.cpu(), Hq, Hkv, D)
+        o = torch.empty_like(c4.q)
+        ms = med(lambda: A.decode_paged(c4.q, c4.k_cache, c4.v_cache, c4.context_lens, c4.block_tables, c4.scale, out=o), 10)
+        res["decode_cfg4_b256"] = {"us": round(ms * 1e3, 1), "GB/s": round(nb / ms / 1e6, 1),
+                                   "frac_of_hbm_peak": round(nb / ms / 1e6 / hbm_peak_gbs, 3)}
+        if fa:
+            bt = c4.block_tables.clamp(min=0)
+            ms = med(lambda: fa.flash_attn_with_kvcache(c4.q.unsqueeze(1), c4.k_cache, c4.v_cache,
+                                                        cache_seqlens=c4.context_lens, block_table=bt,
+                                                        softmax_scale=c4.scale, causal=True), 10)
+            res["flash_attn_decode_cfg4_b256"] = {"us": round(ms * 1e3, 1), "GB/s": round(nb / ms / 1e6, 1),
+                                                  "frac_of_hbm_peak": round(nb / ms / 1e6 / hbm_peak_gbs, 3)}
+        del c4, o
     if only in (None, "decode_long"):
         c5 = W.cfg5_decode(1, dev, batch=256)
         B, Hq, Hkv, D = c5.geometry
@@ -421,6 +459,13 @@ def secondary(dev, hbm_peak_gbs, only=None):
         ms = med(lambda: A.decode_paged(c5.q, c5.k_cache, c5.v_cache, c5.context_lens, c5.block_tables, c5.scale, out=o), 10)
         res["decode_cfg5_b256_ctx32768"] = {"us": round(ms * 1e3, 1), "GB/s": round(nb / ms / 1e6, 1),
                                             "frac_of_hbm_peak": round(nb / ms / 1e6 / hbm_peak_gbs, 3)}
+        if fa:
+            bt = c5.block_tables.clamp(min=0)
+            ms = med(lambda: fa.flash_attn_with_kvcache(c5.q.unsqueeze(1), c5.k_cache, c5.v_cache,
+                                                        cache_seqlens=c5.context_lens, block_table=bt,
+                                                        softmax_scale=c5.scale, causal=True), 10)
+            res["flash_attn_decode_cfg5_b256_ctx32768"] = {"us": round(ms * 1e3, 1), "GB/s": round(nb / ms / 1e6, 1),
+                                                           "frac_of_hbm_peak": round(nb / ms / 1e6 / hbm_peak_gbs, 3)}
     return res
 
 
@@ -430,7 +475,8 @@ def run_one_kernel(args):
     _build.build()
     torch.cuda.set_device(0)
     peak, _ = hbm_peak()
-    print(json.dumps({"kernel": args.kernel, **secondary(torch.device("cuda", 0), peak, only=args.kernel)}), flush=True)
+    print(json.dumps({"kernel": args.kernel, **secondary(torch.device("cuda", 0), peak, only=args.kernel,
+                                                          compare=args.with_flash_attn)}), flush=True)
 
 
 def main():
