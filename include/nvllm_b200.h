@@ -169,6 +169,25 @@ NVLLM_API int nvllm_prefill_varlen(const void* q, int64_t q_row_stride,
                          int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
                          float scale, int64_t num_blocks, void* stream);
 
+/*
+ * Fused pre-attention step over the fused qkv activation [n_tokens, (Hq + 2*Hkv) * D] (bf16,
+ * row stride given): per-head RMSNorm of q and k (skipped when both weights are NULL), NeoX
+ * rotary embedding of q and k from a [max_position, D] fp32 table (cos half, then sin half),
+ * in place; then the rotated k rows and the v rows are copied to their cache slots (skipped
+ * when slot_mapping is NULL; slot < 0 rows are skipped).  positions is int64 [n_tokens].
+ * Replaces, in nano-vllm's attention blocks (nanovllm/models/qwen3.py:89-107,
+ * qwen2.py:87-90): RMSNorm.rms_forward x2 (nanovllm/layers/layernorm.py:17-27),
+ * RotaryEmbedding.forward (nanovllm/layers/rotary_embedding.py:39-55) and store_kvcache
+ * (nanovllm/layers/attention.py:32-39), with the same intermediate roundings.
+ * Supported: D in {64,128}.
+ */
+NVLLM_API int nvllm_qk_norm_rope_store(void* qkv, int64_t row_stride, const int64_t* positions,
+                             const void* q_weight, const void* k_weight,
+                             const float* cos_sin_cache, int64_t max_position, float eps,
+                             const int32_t* slot_mapping, void* k_cache, void* v_cache, int64_t num_slots,
+                             int64_t n_tokens, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                             void* stream);
+
 /* Known-answer check of the tensor-core building blocks the prefill kernel is made of
  * (TMA swizzled loads, shared-memory and instruction descriptors, TMEM loads and stores):
  * out_ss = A B^T and out_ts = A B for A, B [128,128] bf16 row-major, outputs [128,128] fp32.

@@ -30,6 +30,9 @@ SIGNATURES = {
     "nvllm_prefill_varlen": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                                        c_int32, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int32,
                                        c_int32, c_int32, c_int32, c_int32, c_int32, c_float, c_int64, c_void_p]),
+    "nvllm_qk_norm_rope_store": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float,
+                                           c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32,
+                                           c_void_p]),
     "nvllm_selftest_umma": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvllm_selftest_wait_expiry": (c_int32, [c_void_p, c_void_p]),
     "nvllm_last_error": (c_char_p, []),

@@ -198,6 +198,45 @@ def prefill_varlen(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens
     return out
 
 
+def qk_norm_rope_store(qkv: torch.Tensor, positions: torch.Tensor, q_weight: torch.Tensor | None,
+                       k_weight: torch.Tensor | None, cos_sin_cache: torch.Tensor, eps: float,
+                       slot_mapping: torch.Tensor | None, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                       num_q_heads: int, num_kv_heads: int, head_dim: int) -> None:
+    """In place on the fused ``qkv`` activation ``[N, (Hq + 2*Hkv) * D]``: per-head RMSNorm of
+    q and k (when weights are given), rotary embedding of q and k, and the scatter of the new
+    K/V rows into the cache (when ``slot_mapping`` is given and the cache exists).
+
+    One launch for what nanovllm/models/qwen3.py:89-107 does with ``q_norm``, ``k_norm``,
+    ``rotary_emb`` and, inside the attention layer, ``store_kvcache``.
+    """
+    _require_cuda_bf16("qkv", qkv)
+    assert qkv.dim() == 2 and qkv.stride(-1) == 1
+    assert qkv.shape[1] == (num_q_heads + 2 * num_kv_heads) * head_dim
+    assert positions.is_cuda and positions.dtype == torch.int64 and positions.numel() == qkv.shape[0]
+    assert cos_sin_cache.is_cuda and cos_sin_cache.dtype == torch.float32 and cos_sin_cache.is_contiguous()
+    cs = cos_sin_cache.view(-1, head_dim)
+    for w in (q_weight, k_weight):
+        if w is not None:
+            _require_cuda_bf16("norm weight", w)
+            assert w.numel() == head_dim and w.is_contiguous()
+    store = slot_mapping is not None and k_cache.numel() > 0 and v_cache.numel() > 0
+    if store:
+        _require_i32("slot_mapping", slot_mapping)
+        _require_cuda_bf16("k_cache", k_cache)
+        _require_cuda_bf16("v_cache", v_cache)
+        assert k_cache.is_contiguous() and v_cache.is_contiguous() and slot_mapping.numel() == qkv.shape[0]
+    num_slots = k_cache.numel() // (num_kv_heads * head_dim) if store else 0
+    with torch.cuda.device(qkv.device):
+        _lib.check(_lib.load().nvllm_qk_norm_rope_store(
+            qkv.data_ptr(), qkv.stride(0), positions.data_ptr(),
+            q_weight.data_ptr() if q_weight is not None else None,
+            k_weight.data_ptr() if k_weight is not None else None,
+            cs.data_ptr(), cs.shape[0], float(eps),
+            slot_mapping.data_ptr() if store else None,
+            k_cache.data_ptr() if store else None, v_cache.data_ptr() if store else None, num_slots,
+            qkv.shape[0], num_q_heads, num_kv_heads, head_dim, _stream(qkv)))
+
+
 # ---- the layer --------------------------------------------------------------------------
 
 class Attention(nn.Module):
@@ -211,13 +250,15 @@ class Attention(nn.Module):
         self.num_kv_heads = num_kv_heads
         self.k_cache = self.v_cache = torch.tensor([])
 
-    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kv_stored: bool = False):
+        """``kv_stored=True``: the caller has already written this step's K/V rows into the cache
+        (the fused pre-attention step does); the reference signature is ``forward(q, k, v)``."""
         q = q.view(-1, self.num_heads, self.head_dim)
         k = k.view(-1, self.num_kv_heads, self.head_dim)
         v = v.view(-1, self.num_kv_heads, self.head_dim)
         context = _get_context()
         k_cache, v_cache = self.k_cache, self.v_cache
-        if k_cache.numel() and v_cache.numel():
+        if k_cache.numel() and v_cache.numel() and not kv_stored:
             store_kvcache(k, v, k_cache, v_cache, context.slot_mapping)
         if context.is_prefill:
             if context.block_tables is not None:  # prefix cache: read every key through the table

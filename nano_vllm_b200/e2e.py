@@ -79,9 +79,11 @@ def apply_shims(attn: str, ref_path: str):
         sys.path.insert(0, ref_path)
     if str(ROOT) not in sys.path:
         sys.path.insert(0, str(ROOT))
-    if attn == "b200":
+    if attn in ("b200", "b200-fused"):
         from nano_vllm_b200 import plugin
         plugin.install()
+        if attn == "b200-fused":
+            plugin.fuse_pre_attention()
     import nanovllm.engine.model_runner as mr
     mr.load_model = random_init
 
@@ -132,7 +134,9 @@ def make_engine(model_dir: str, attn: str, ref_path: str, **kwargs):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--attn", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--attn", default="b200", choices=["b200", "b200-fused", "reference"],
+                    help="b200: swap the attention layer; b200-fused: also fuse q/k norm + rotary + store; "
+                         "reference: stock nano-vllm")
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--model", default="qwen3-0.6b", choices=sorted(GEOMETRY))
     ap.add_argument("--num-seqs", type=int, default=256)
@@ -176,7 +180,7 @@ def main():
             "model": args.model + " (random init)", "tp": args.tp, "num_seqs": args.num_seqs,
             "output_tokens": total, "tokens_returned": got, "prompt_tokens": sum(map(len, prompts)),
             "seconds": round(dt, 3), "engine_init_s": round(init_s, 1), "cuda_graphs": not args.enforce_eager}
-    if args.attn == "b200":
+    if args.attn != "reference":
         from nano_vllm_b200 import _lib
         line["kernel_launches"] = _lib.launch_count()
         line["device_status_word"] = _lib.read_status()

@@ -18,6 +18,35 @@ from . import attention as _attention
 MODULE_NAME = "nanovllm.layers.attention"
 
 
+def _fused_attention_forward(has_qk_norm: bool):
+    """Replacement for Qwen3Attention.forward / Qwen2Attention.forward
+    (nanovllm/models/qwen3.py:77-113, qwen2.py:77-97): same projections, but q/k norm, rotary
+    embedding and the KV-cache store run as one launch on the fused qkv activation."""
+
+    def forward(self, positions, hidden_states):
+        qkv = self.qkv_proj(hidden_states)
+        attn = self.attn
+        ctx = _attention._get_context()
+        _attention.qk_norm_rope_store(
+            qkv, positions,
+            self.q_norm.weight if has_qk_norm else None, self.k_norm.weight if has_qk_norm else None,
+            self.rotary_emb.cos_sin_cache, self.q_norm.eps if has_qk_norm else 0.0,
+            ctx.slot_mapping, attn.k_cache, attn.v_cache, self.num_heads, self.num_kv_heads, self.head_dim)
+        q, k, v = qkv.split([self.q_size, self.kv_size, self.kv_size], dim=-1)
+        return self.o_proj(attn(q, k, v, kv_stored=True))
+
+    return forward
+
+
+def fuse_pre_attention() -> None:
+    """Optional second step after ``install()``: also replace the q/k-norm + rotary + store
+    sequence of nano-vllm's Qwen3 and Qwen2 attention blocks by the fused kernel."""
+    qwen3 = importlib.import_module("nanovllm.models.qwen3")
+    qwen2 = importlib.import_module("nanovllm.models.qwen2")
+    qwen3.Qwen3Attention.forward = _fused_attention_forward(True)
+    qwen2.Qwen2Attention.forward = _fused_attention_forward(False)
+
+
 def install() -> types.ModuleType:
     already = sys.modules.get(MODULE_NAME)
     if already is not None and getattr(already, "__nano_vllm_b200__", False):

@@ -110,3 +110,42 @@ def attention_forward_ref(q, k, v, k_cache, v_cache, ctx, scale):
             return prefill_ref(q, k_cache, v_cache, ctx.cu_seqlens_q, ctx.cu_seqlens_k, scale, ctx.block_tables)
         return prefill_ref(q, k, v, ctx.cu_seqlens_q, ctx.cu_seqlens_k, scale)
     return decode_ref(q, k_cache, v_cache, ctx.context_lens, ctx.block_tables, scale)
+
+
+# ---- pre-attention step (q/k RMSNorm + rotary embedding) ------------------------------------
+
+def rms_norm_ref(x, weight, eps):
+    """nanovllm/layers/layernorm.py:17-27 (RMSNorm.rms_forward) with its roundings: fp32
+    normalisation, cast to the input dtype, then the multiply by the weight in that dtype."""
+    orig = x.dtype
+    xf = x.to(torch.float32)
+    var = xf.pow(2).mean(dim=-1, keepdim=True)
+    xf = xf * torch.rsqrt(var + eps)
+    return xf.to(orig) * weight
+
+
+def rotary_cache_ref(head_dim, max_position, base):
+    """nanovllm/layers/rotary_embedding.py:28-37: [max_position, head_dim] fp32, cos then sin."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, head_dim, 2, dtype=torch.float) / head_dim))
+    t = torch.arange(max_position, dtype=torch.float)
+    freqs = torch.einsum("i,j -> ij", t, inv_freq)
+    return torch.cat((freqs.cos(), freqs.sin()), dim=-1)
+
+
+def apply_rotary_ref(x, cos, sin):
+    """nanovllm/layers/rotary_embedding.py:6-16 (NeoX style: the two halves of a head rotate)."""
+    cos, sin = cos.unsqueeze(-2), sin.unsqueeze(-2)
+    x1, x2 = torch.chunk(x.to(torch.float32), 2, dim=-1)
+    return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1).to(x.dtype)
+
+
+def qk_norm_rope_ref(qkv, positions, q_weight, k_weight, cos_sin_cache, eps, hq, hkv, d):
+    """The q/k path of nanovllm/models/qwen3.py:89-105 (weights None: qwen2.py:87-90) on a CPU
+    copy of the fused qkv activation.  Returns (q [N,hq,d], k [N,hkv,d], v [N,hkv,d])."""
+    n = qkv.shape[0]
+    q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
+    q, k, v = q.reshape(n, hq, d), k.reshape(n, hkv, d), v.reshape(n, hkv, d)
+    if q_weight is not None:
+        q, k = rms_norm_ref(q, q_weight, eps), rms_norm_ref(k, k_weight, eps)
+    cos, sin = cos_sin_cache[positions].chunk(2, dim=-1)
+    return apply_rotary_ref(q, cos, sin), apply_rotary_ref(k, cos, sin), v
