@@ -57,6 +57,8 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=256, help="sequences in the decode batch")
     ap.add_argument("--no-secondary", action="store_true", help="skip the store/prefill/long-context extras")
+    ap.add_argument("--no-engine", action="store_true",
+                    help="skip the end-to-end nano-vllm engine run (output tok/s) that follows at 1 GPU")
     ap.add_argument("--kernel", default=None, choices=["prefill", "prefill_long", "prefill_d64", "store", "decode", "decode_long"],
                     help="time only this secondary kernel on one GPU and print its line (profiling aid)")
     ap.add_argument("--with-flash-attn", action="store_true",
@@ -335,6 +337,10 @@ def run_ours(args):
         if not args.no_secondary:
             del sample_case
             line["secondary"] = secondary(dev, peak)
+        if not args.no_engine and not args.no_secondary:
+            del case, out
+            torch.cuda.empty_cache()
+            line["engine_tok_per_s"] = engine_run()
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -467,6 +473,25 @@ def secondary(dev, hbm_peak_gbs, only=None, compare=False):
             res["flash_attn_decode_cfg5_b256_ctx32768"] = {"us": round(ms * 1e3, 1), "GB/s": round(nb / ms / 1e6, 1),
                                                            "frac_of_hbm_peak": round(nb / ms / 1e6 / hbm_peak_gbs, 3)}
     return res
+
+
+def engine_run():
+    """Output tok/s of the unmodified nano-vllm engine (installed under baseline/_ref) with the
+    B200 attention layer swapped in: the reference's own benchmark workload on random-init
+    Qwen3-0.6B, 1 GPU (python -m nano_vllm_b200.e2e).  Runs as a child process with a time limit;
+    any failure is reported as a string instead of a number."""
+    if not (ROOT / "baseline" / "_ref" / "nanovllm").is_dir():
+        return {"unavailable": "no nano-vllm install under baseline/_ref"}
+    try:
+        proc = subprocess.run([sys.executable, "-m", "nano_vllm_b200.e2e", "--attn", "b200-fused"], cwd=str(ROOT),
+                              capture_output=True, text=True, timeout=420)
+        for ln in reversed(proc.stdout.strip().splitlines()):
+            if ln.startswith("{"):
+                d = json.loads(ln)
+                return {k: d[k] for k in ("value", "unit", "model", "num_seqs", "output_tokens", "seconds", "attn") if k in d}
+        return {"unavailable": (proc.stderr or proc.stdout)[-300:]}
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": repr(e)[:300]}
 
 
 def run_one_kernel(args):

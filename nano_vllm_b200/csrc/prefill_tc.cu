@@ -32,20 +32,6 @@
 namespace nvllm {
 using namespace sm100;
 
-#ifdef NVLLM_PHASE_CLOCKS
-// Development aid: per-tile clock64() stamps of one block's softmax thread 0 and MMA thread.
-__device__ long long g_phase_clocks[64 * 12];
-__device__ int g_dev_mode = 0;  // 1: softmax does no TMEM traffic and no math; 2: TMEM traffic only
-#define PHASE_STAMP(j, k)                                                    \
-  do {                                                                       \
-    if (prof_block && (j) < 64) g_phase_clocks[(j) * 12 + (k)] = clock64();  \
-  } while (0)
-#else
-#define PHASE_STAMP(j, k) \
-  do {                    \
-  } while (0)
-#endif
-
 __global__ void __launch_bounds__(tc::NTHREADS, 2)
 prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tmap_q,
                   const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v) {
@@ -64,17 +50,12 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
   if (kv_end < 0) kv_end = 0;
   const int n_kv = (kv_end + BN - 1) / BN;
 
-#ifdef NVLLM_PHASE_CLOCKS
-  const bool prof_block = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (tid == 0 || tid == 160);
-#endif
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t bars = base + OFF_BAR;
   auto bar = [&](int i) { return bars + 8u * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + OFF_BAR + 8 * NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + OFF_BAR + 8 * NUM_BARS + 8);
-
-  PHASE_STAMP(63, 0);
   // Loads of K/V tile j into ring stage j&1 (producer lane only).
   const int32_t* bt_row = p.block_tables ? p.block_tables + b * p.bt_stride : nullptr;
   auto kv_row = [&](int j) -> int {
@@ -122,7 +103,6 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tmem_o = tmem + 128;
-  PHASE_STAMP(63, 1);
 
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
@@ -152,7 +132,6 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
       auto issue_qk = [&](int j) -> bool {
         const int st = j & 1;
         if (!wait_or_abort(bar(K_FULL0 + st), (j >> 1) & 1, abort_flag)) return false;
-        PHASE_STAMP(j - 1, 10);
         tc_fence_after();
         const uint64_t kd = k_desc + static_cast<uint64_t>(st * (KV_BYTES >> 4));
         const uint32_t d_tmem = tmem + st * 64;
@@ -166,17 +145,12 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
         return true;
       };
       bool ok = wait_or_abort(bar(Q_FULL), 0, abort_flag);
-      PHASE_STAMP(63, 2);
       ok = ok && issue_qk(0);
-      PHASE_STAMP(63, 3);
       for (int j = 0; ok && j < n_kv; ++j) {
         const int st = j & 1, ph = (j >> 1) & 1;
-        PHASE_STAMP(j, 9);
         if (j + 1 < n_kv && !(ok = issue_qk(j + 1))) break;  // next S runs under this tile's softmax
-        PHASE_STAMP(j, 6);
         if (!(ok = wait_or_abort(bar(V_FULL0 + st), ph, abort_flag))) break;
         if (!(ok = wait_or_abort(bar(P_FULL0 + st), ph, abort_flag))) break;
-        PHASE_STAMP(j, 7);
         tc_fence_after();
         const uint64_t vd = v_desc + static_cast<uint64_t>(st * (KV_BYTES >> 4));
         const uint32_t p_tmem = tmem + st * 64;
@@ -184,7 +158,6 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
         for (int ks = 0; ks < BN / 16; ++ks)
           umma_ts(tmem_o, p_tmem + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
         umma_commit(bar(PV_DONE0 + st));
-        PHASE_STAMP(j, 8);
       }
       if (!ok) {  // make sure nothing is still running on TMEM before it is freed
         umma_commit(bar(DRAIN));
@@ -201,35 +174,12 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
     for (int j = 0; j < n_kv; ++j) {
       const int st = j & 1, ph = (j >> 1) & 1;
       const uint32_t tmem_s = tmem + st * 64 + lane_addr;
-      PHASE_STAMP(j, 0);
       if (!(ok = wait_or_abort(bar(QK_DONE0 + st), ph, abort_flag))) break;
-      PHASE_STAMP(j, 1);
       tc_fence_after();
-#ifdef NVLLM_PHASE_CLOCKS
-      if (g_dev_mode == 1) {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(P_FULL0 + st));
-        continue;
-      }
-      if (g_dev_mode == 2) {
-        uint32_t t[32];
-        tmem_ld32(tmem_s, t);
-        tmem_ld32(tmem_s + 32, t);
-        tmem_wait_ld();
-        tmem_st32(tmem_s, t);
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(P_FULL0 + st));
-        continue;
-      }
-#endif
       uint32_t s[64];
       tmem_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       tmem_ld32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
       tmem_wait_ld();
-      PHASE_STAMP(j, 2);
 
       const int j0 = j * BN;
       if ((j0 + BN - 1 > m0 + off) || (j0 + BN > Lk)) {  // tile touches the diagonal or the end
@@ -266,7 +216,6 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
           }
         }
       }
-      PHASE_STAMP(j, 3);
       const float msub = (m_used == -INFINITY) ? 0.f : m_used;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -290,15 +239,12 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
         }
         fence_proxy_async();
       }
-      PHASE_STAMP(j, 4);
       tmem_st32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(P_FULL0 + st));
-      PHASE_STAMP(j, 5);
     }
-    PHASE_STAMP(63, 4);
     // epilogue: O / l -> bf16 -> global (rows past the sequence end are not written)
     if (ok && n_kv > 0) ok = wait_or_abort(bar(PV_DONE0 + ((n_kv - 1) & 1)), ((n_kv - 1) >> 1) & 1, abort_flag);
     tc_fence_after();
@@ -338,20 +284,13 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tma
             *reinterpret_cast<const uint4*>(stage + row * 256 + ((cc ^ (row & 15)) << 4));
     }
   }
-
-  PHASE_STAMP(63, 5);
   tc_fence_before();
   __syncthreads();
-  PHASE_STAMP(63, 6);
   if (tid == 0 && *abort_flag) atomicOr(p.status, NVLLM_STATUS_TIMEOUT);
   if (warp == 5) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
-  PHASE_STAMP(63, 7);
-#ifdef NVLLM_PHASE_CLOCKS
-  if (prof_block && tid == 0) g_phase_clocks[63 * 12 + 8] = n_kv;
-#endif
 }
 
 // ---- known-answer check of the building blocks --------------------------------------------
@@ -511,27 +450,12 @@ int launch_prefill_tc(const PrefillParams& p, int64_t total_q, int64_t total_k, 
     if (!make_tmap_3d(&mv, p.v, tc::D, p.hkv, total_k, tc::D, p.v_stride, tc::BN)) return NVLLM_E_CUDA;
   }
   dim3 grid((p.max_seqlen_q + tc::BM - 1) / tc::BM, p.hq, p.batch);
-#ifdef NVLLM_PHASE_CLOCKS
-  static const int pad = std::getenv("NVLLM_TC_SMEM_PAD") ? std::atoi(std::getenv("NVLLM_TC_SMEM_PAD")) : 0;
-  static const int mode = std::getenv("NVLLM_TC_MODE") ? std::atoi(std::getenv("NVLLM_TC_MODE")) : 0;
-  cudaMemcpyToSymbol(g_dev_mode, &mode, sizeof(int));
-  if (pad) cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, tc::SMEM + pad);
-  prefill_tc_kernel<<<grid, tc::NTHREADS, tc::SMEM + pad, stream>>>(p, mq, mk, mv);
-  count_launch();
-  return check_launch("prefill (tcgen05) launch");
-#endif
   prefill_tc_kernel<<<grid, tc::NTHREADS, tc::SMEM, stream>>>(p, mq, mk, mv);
   count_launch();
   return check_launch("prefill (tcgen05) launch");
 }
 
 }  // namespace nvllm
-
-#ifdef NVLLM_PHASE_CLOCKS
-extern "C" __attribute__((visibility("default"))) int nvllm_debug_phase_clocks(long long* host_out) {
-  return cudaMemcpyFromSymbol(host_out, nvllm::g_phase_clocks, sizeof(long long) * 64 * 12) == cudaSuccess ? 0 : -5;
-}
-#endif
 
 extern "C" int nvllm_selftest_wait_expiry(int32_t* device_result, void* stream) {
   using namespace nvllm;
