@@ -276,15 +276,31 @@ def run_ours(args):
     status = _lib.read_status()
 
     # ---- end to end from pinned host buffers
-    host = {k: getattr(case, k).cpu().pin_memory() for k in ("q", "k_new", "v_new", "slot_mapping", "context_lens", "block_tables")}
-    devbuf = {k: torch.empty_like(getattr(case, k)) for k in host}
+    # The step's inputs (q, the new K/V rows, slot ids, lengths, block table) sit in ONE pinned
+    # host staging block and go over in one copy; the device tensors are views of its device twin.
+    names = ("q", "k_new", "v_new", "slot_mapping", "context_lens", "block_tables")
+    offs, total = {}, 0
+    for k in names:
+        t = getattr(case, k)
+        offs[k] = total
+        total += (t.numel() * t.element_size() + 255) // 256 * 256
+    host_block = torch.empty(total, dtype=torch.uint8).pin_memory()
+    dev_block = torch.empty(total, dtype=torch.uint8, device=dev)
+
+    def view(block, k):
+        t = getattr(case, k)
+        n = t.numel() * t.element_size()
+        return block[offs[k]:offs[k] + n].view(t.dtype).view(t.shape)
+
+    for k in names:
+        view(host_block, k).copy_(getattr(case, k).cpu())
+    devbuf = {k: view(dev_block, k) for k in names}
     out_host = torch.empty(out.shape, dtype=out.dtype).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    h2d = sum(getattr(case, k).numel() * getattr(case, k).element_size() for k in names)
     d2h = out_host.numel() * out_host.element_size()
 
     def e2e_step():
-        for k, t in host.items():
-            devbuf[k].copy_(t, non_blocking=True)
+        dev_block.copy_(host_block, non_blocking=True)
         A.store_kvcache(devbuf["k_new"], devbuf["v_new"], case.k_cache, case.v_cache, devbuf["slot_mapping"])
         A.decode_paged(devbuf["q"], case.k_cache, case.v_cache, devbuf["context_lens"], devbuf["block_tables"], case.scale, out=out)
         out_host.copy_(out, non_blocking=True)
