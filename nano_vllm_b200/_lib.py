@@ -6,10 +6,9 @@ Loading fails loudly if the library has not been built (``python -m nano_vllm_b2
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_char_p, c_float, c_int32, c_int64, c_void_p, POINTER
 from pathlib import Path
-
-import os
 
 # NVLLM_B200_LIB points the loader at another build of the same library (e.g. one compiled
 # with development instrumentation); by default the in-tree build is used.
