@@ -1,0 +1,65 @@
+"""The import-time swap of nano-vllm's attention layer (plugin.install) against an installed
+copy of the reference (baseline/_ref, made with pip --target; skipped when it is absent).
+Runs in child processes because the swap must happen before anything of nanovllm is imported."""
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+REF = ROOT / "baseline" / "_ref"
+
+pytestmark = pytest.mark.skipif(not (REF / "nanovllm").is_dir(), reason="no nano-vllm install under baseline/_ref")
+
+
+def _run(code: str) -> str:
+    proc = subprocess.run([sys.executable, "-c", code], cwd=str(ROOT), capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    return proc.stdout.strip().splitlines()[-1]
+
+
+PRELUDE = f"import sys; sys.path.insert(0, {str(REF)!r}); sys.path.insert(0, {str(ROOT)!r})\n"
+
+
+def test_install_replaces_the_layer_the_models_bind():
+    out = _run(PRELUDE + """
+from nano_vllm_b200 import plugin, attention
+plugin.install()
+import nanovllm.models.qwen3 as q3, nanovllm.models.qwen2 as q2
+from nanovllm.utils.context import set_context, get_context
+import nanovllm.layers.attention as mod
+assert q3.Attention is attention.Attention and q2.Attention is attention.Attention
+assert mod.store_kvcache is attention.store_kvcache
+set_context(True, max_seqlen_q=7)
+assert attention._get_context().max_seqlen_q == 7      # the layer reads the engine's own context
+assert "flash_attn" not in sys.modules                  # the attention path no longer imports it
+print("ok")
+""")
+    assert out == "ok"
+
+
+def test_install_refuses_to_run_after_the_models_were_imported():
+    out = _run(PRELUDE + """
+import nanovllm                      # binds the stock layer
+from nano_vllm_b200 import plugin
+try:
+    plugin.install()
+    print("no error")
+except RuntimeError as e:
+    print("refused")
+""")
+    assert out == "refused"
+
+
+def test_fuse_pre_attention_swaps_the_attention_blocks_forward():
+    out = _run(PRELUDE + """
+from nano_vllm_b200 import plugin
+plugin.install()
+import nanovllm.models.qwen3 as q3, nanovllm.models.qwen2 as q2
+before = q3.Qwen3Attention.forward
+plugin.fuse_pre_attention()
+assert q3.Qwen3Attention.forward is not before and q2.Qwen2Attention.forward.__name__ == "forward"
+print("ok")
+""")
+    assert out == "ok"
