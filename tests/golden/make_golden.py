@@ -90,4 +90,4 @@ def main(out_dir: Path) -> None:
 
 
 if __name__ == "__main__":
-    main(Path(sys.argv[1]) if len(sys.argv) > 1 else C.ROOT / "gpurun_out" / "golden")
+    main(Path(sys.argv[1]) if len(sys.argv) > 1 else C.GOLDEN_DIR)

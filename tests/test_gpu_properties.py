@@ -1,6 +1,6 @@
 """Property tests over random lengths, prefix hits and scattered block tables, and canary
-checks that no kernel writes outside the rows it owns (there is no memory checker on the GPU
-boxes, so out-of-bounds writes are looked for with sentinels around every output)."""
+checks that no kernel writes outside the rows it owns (no memory checker is available where these
+tests run, so out-of-bounds writes are looked for with sentinels around every output)."""
 import pytest
 import torch
 from hypothesis import given, settings, strategies as st, HealthCheck
