@@ -107,3 +107,30 @@ def test_strided_q_and_cuda_graph_replay(cuda):
     torch.cuda.synchronize()
     ref = R.decode_ref(case.q, case.k_cache, case.v_cache, case.context_lens, case.block_tables, case.scale)
     assert_close_to_oracle(out, ref, "graph replay")
+
+
+@pytest.mark.parametrize("tp", [2, 4, 8])
+def test_head_sharded_ranks_reassemble_the_unsharded_result(cuda, tp):
+    """Tensor parallelism: rank r holds query heads [r*Hq/tp, ...) and KV heads [r*Hkv/tp, ...) of
+    every cache row (nanovllm/engine/model_runner.py:117, nanovllm/layers/linear.py:141-163) and
+    sees identical metadata.  All shards run here on one GPU, one after the other; their outputs
+    side by side must equal the unsharded kernel's output bit for bit (same arithmetic per head)
+    and match the oracle."""
+    hq, hkv, d = 32, 8, 128
+    case = W.make_decode_case(18, 6, 1, 1, hq, hkv, d, context_lens=[700, 1, 2049, 256, 3000, 513], table_width=12)
+    dev = case.to(cuda)
+    full = A.decode_paged(dev.q, dev.k_cache, dev.v_cache, dev.context_lens, dev.block_tables, case.scale)
+    parts = []
+    for r in range(tp):
+        qs = dev.q[:, r * hq // tp:(r + 1) * hq // tp].contiguous()
+        ks = dev.k_cache[:, :, r * hkv // tp:(r + 1) * hkv // tp].contiguous()
+        vs = dev.v_cache[:, :, r * hkv // tp:(r + 1) * hkv // tp].contiguous()
+        parts.append(A.decode_paged(qs, ks, vs, dev.context_lens, dev.block_tables, case.scale))
+    torch.cuda.synchronize()
+    ref = R.decode_ref(case.q, case.k_cache, case.v_cache, case.context_lens, case.block_tables, case.scale)
+    assert_close_to_oracle(torch.cat(parts, dim=1), ref, f"tp{tp}")
+    # per-head arithmetic does not depend on how many heads share the launch as long as the split
+    # plan is the same; the plan depends on batch*Hkv, so compare against the oracle above and
+    # check exact equality only where the plans agree
+    if _lib.decode_plan(6, 12, hq // tp, hkv // tp, d) == _lib.decode_plan(6, 12, hq, hkv, d):
+        assert torch.equal(torch.cat(parts, dim=1), full)
