@@ -25,6 +25,18 @@
 
 #include "common.cuh"
 
+// Pipeline shape of the head_dim-128 kernel: tokens per warp tile, ring stages per warp, warps per
+// block (overridable at build time for sweeps; the defaults are the measured best).
+#ifndef NVLLM_DEC_TT
+#define NVLLM_DEC_TT 16
+#endif
+#ifndef NVLLM_DEC_NST
+#define NVLLM_DEC_NST 3
+#endif
+#ifndef NVLLM_DEC_NW
+#define NVLLM_DEC_NW 4
+#endif
+
 namespace nvllm {
 
 struct DecodeParams {
@@ -456,7 +468,7 @@ extern "C" int nvllm_decode_paged(const void* q, int64_t q_row_stride, const voi
   p.ws_ml = need > 0 ? p.ws_o + rows * head_dim : nullptr;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (head_dim == 128) return launch_decode<DecodeCfg<128, 16, 3, 4>>(p, st);
+  if (head_dim == 128) return launch_decode<DecodeCfg<128, NVLLM_DEC_TT, NVLLM_DEC_NST, NVLLM_DEC_NW>>(p, st);
   return launch_decode<DecodeCfg<64, 32, 3, 4>>(p, st);
 }
 
