@@ -1,10 +1,13 @@
-// Persistent variant of the tcgen05 prefill kernel (head_dim 128).
+// Persistent variant of the tcgen05 prefill kernel (head_dim 64 or 128).
 //
 // Same tile pipeline as prefill_tc.cu (128 query rows x 64-key tiles, S double-buffered in
 // TMEM, P fed back from TMEM, two-stage K/V ring, one commit per MMA group), but a thread
 // block does not end with its query tile: two blocks per SM stay resident for the whole launch,
-// keep their TMEM allocation and barriers, and pull work items (sequence, query tile, head)
-// from a global counter.  What this buys on short prompts, where a block only has a handful of
+// keep their TMEM allocation and barriers, and pull work items (sequence, query tile, head
+// group) from a global counter.  Under grouped-query attention the 128 rows of a tile are
+// 128/n tokens x n query heads that share a KV head (n = 1, 2, 4 or 8), not 128 tokens of one
+// head: the causal diagonal and the ragged end of a sequence then cut through a narrower band
+// of tokens, so fewer of the issued products are masked or padding.  What this buys on short prompts, where a block only has a handful of
 // key tiles: the block launch / TMEM allocation / barrier set-up is paid once, the producer
 // lane fetches the next item and starts its Q and first K loads while the current item is
 // still in its last softmax, and the tensor pipe runs the next item's first S product under
@@ -12,10 +15,12 @@
 //
 // Item hand-off: the producer lane decodes an item into one of two descriptor slots in shared
 // memory (ITEM_FULL / ITEM_FREE barriers).  All rings keep running across items: tile t of the
-// block's life uses stage t&1 and barrier phase (t>>1)&1.  The epilogue stages O through the
-// V ring (free once the item's last P V product is complete), so the producer holds back only
-// the next item's first two V tiles (STAGE_FREE); the first P V product of an item waits
-// for the previous item's O to be read (O_FREE).
+// block's life uses stage t&1 and barrier phase (t>>1)&1, so the next item's first K/V tiles
+// are fetched under the current item's last products.  The first P V product of an item waits
+// for the previous item's O to be read (O_FREE).  The epilogue needs no block-wide buffer: a
+// softmax warp owns the same 32 rows in TMEM and in the output, and passes them 32 columns at
+// a time through a private 2 KB patch of shared memory to turn row-per-lane registers into
+// 64-byte row segments.
 #include <atomic>
 #include <cstdlib>
 
@@ -31,7 +36,7 @@ namespace tcp {
 using namespace tc;
 constexpr int MAX_BATCH = 1024;  // prefix array of query tiles per sequence lives in shared memory
 enum PBar {
-  ITEM_FULL0 = tc::NUM_BARS, ITEM_FULL1, ITEM_FREE0, ITEM_FREE1, O_FREE, STAGE_FREE, P_NUM_BARS
+  ITEM_FULL0 = tc::NUM_BARS, ITEM_FULL1, ITEM_FREE0, ITEM_FREE1, O_FREE, P_NUM_BARS
 };
 // Shared-memory layout and tile sizes for one head_dim (64 or 128).  A tile row is split into
 // 64-element (128-byte) sub-tiles, the unit of the 128-byte swizzle.
@@ -42,7 +47,8 @@ struct Geo {
   static constexpr int Q_SUB = BM * 128, Q_BYTES = NSUB * Q_SUB;
   static constexpr int KV_SUB = BN * 128, KV_BYTES = NSUB * KV_SUB;
   static constexpr int OFF_Q = 0, OFF_K = Q_BYTES, OFF_V = OFF_K + KST * KV_BYTES;
-  static constexpr int OFF_CTRL = OFF_V + KST * KV_BYTES;  // barriers (8 B each)
+  static constexpr int OFF_STAGE = OFF_V + KST * KV_BYTES;  // 4 warps x 32 rows x 64 B of output
+  static constexpr int OFF_CTRL = OFF_STAGE + 4 * 2048;     // barriers (8 B each)
   static constexpr int OFF_SLOTS = OFF_CTRL + 256;         // two item descriptors of 8 ints
   static constexpr int OFF_MISC = OFF_SLOTS + 64;          // tmem address, abort flag
   static constexpr int OFF_PREFIX = OFF_MISC + 64;         // (MAX_BATCH + 1) ints
@@ -50,7 +56,6 @@ struct Geo {
   static constexpr int OCH = D / 32;      // 32-column chunks of O
   static constexpr int ROWB = D * 2;      // bytes of one output row
   static constexpr int PIECES = D / 8;    // 16-byte pieces of one row
-  static_assert(BM * ROWB == KST * KV_BYTES, "the epilogue stages O through the whole V ring");
 };
 constexpr int NUM_SLOTS = 64;                     // launches that may be in flight at once
 static_assert(P_NUM_BARS * 8 <= 256, "barrier area");
@@ -86,6 +91,11 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + OFF_MISC + 8);
   int* prefix = reinterpret_cast<int*>(base_ptr + OFF_PREFIX);  // prefix[b] = query tiles before sequence b
+  // Head packing: the 128 rows of a tile are BMT = 128 >> pl query tokens x (1 << pl) query heads
+  // of one KV head (row = token * heads + head), so short and ragged sequences waste fewer rows
+  // above the diagonal and past their end, and the packed heads share every K/V tile.
+  static_assert(BM == 128, "the tile-count shift below assumes 128 rows");
+  const int pl = p.pack_log2, BMT = BM >> pl;
 
   if (warp == 4) {
     // query tiles per sequence -> exclusive prefix sum (warp scan, 32 sequences at a time)
@@ -93,7 +103,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
     for (int b0 = 0; b0 < p.batch; b0 += 32) {
       const int b = b0 + lane;
       int tiles = 0;
-      if (b < p.batch) tiles = (p.cu_q[b + 1] - p.cu_q[b] + BM - 1) / BM;
+      if (b < p.batch) tiles = (p.cu_q[b + 1] - p.cu_q[b] + BMT - 1) >> (7 - pl);
       int incl = tiles;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
@@ -106,7 +116,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
     if (lane == 0) {
       prefix[p.batch] = carry;
       for (int i = 0; i < P_NUM_BARS; ++i) {
-        const uint32_t count = (i == P_FULL0 || i == P_FULL1 || i == O_FREE || i == STAGE_FREE) ? 4u
+        const uint32_t count = (i == P_FULL0 || i == P_FULL1 || i == O_FREE) ? 4u
                                : (i == ITEM_FREE0 || i == ITEM_FREE1)                            ? 5u
                                                                                                  : 1u;
         mbar_init(bar(i), count);
@@ -136,7 +146,8 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
   if (warp == 4) {
     // ------------------------------------------------------------------ producer lane
     if (lane == 0) {
-      const int total_items = prefix[p.batch] * p.hq;
+      const int hgroups = p.hq >> pl;
+      const int total_items = prefix[p.batch] * hgroups;
       int T = 0;   // key tiles loaded so far in this block's life
       int nq = 0;  // items with at least one key tile so far (Q_FULL phase)
       for (int it = 0;; ++it) {
@@ -147,8 +158,8 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
           x.n_kv = -1;
           const unsigned idx = atomicAdd(&g_item_counter[counter_slot], 1u);
           if (idx >= static_cast<unsigned>(total_items)) break;
-          const int pi = idx / p.hq;
-          x.h = idx - pi * p.hq;
+          const int pi = idx / hgroups;
+          x.h = (idx - pi * hgroups) << pl;  // first of the packed heads
           int lo = 0, hi = p.batch;  // largest b with prefix[b] <= pi
           while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
@@ -160,15 +171,15 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
           x.k0 = p.cu_k[lo];
           x.Lk = p.cu_k[lo + 1] - x.k0;
           const int tiles = prefix[lo + 1] - prefix[lo];
-          x.m0 = (tiles - 1 - (pi - prefix[lo])) * BM;  // a sequence's long tiles first
-          const int kv_end = min(x.Lk, min(x.m0 + BM, x.Lq) + (x.Lk - x.Lq));
+          x.m0 = (tiles - 1 - (pi - prefix[lo])) * BMT;  // a sequence's long tiles first
+          const int kv_end = min(x.Lk, min(x.m0 + BMT, x.Lq) + (x.Lk - x.Lq));
           x.n_kv = kv_end > 0 ? (kv_end + BN - 1) / BN : 0;
           if (x.n_kv > 0) break;
           // No visible key for the whole tile (only possible when Lk < Lq, which the engine
           // never produces): the rows are zero; written here, the other roles never see it.
-          for (int r = x.m0; r < min(x.m0 + BM, x.Lq); ++r) {
+          for (int r = x.m0; r < min(x.m0 + BMT, x.Lq); ++r) {
             uint4* dst = reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(x.q0 + r) * p.out_stride + x.h * D);
-            for (int c = 0; c < PIECES; ++c) dst[c] = make_uint4(0, 0, 0, 0);
+            for (int c = 0; c < (PIECES << pl); ++c) dst[c] = make_uint4(0, 0, 0, 0);  // the packed heads are adjacent
           }
         }
         if (it >= 2 && !wait_or_abort(bar(ITEM_FREE0 + (it & 1)), ((it >> 1) - 1) & 1, abort_flag)) break;
@@ -205,8 +216,6 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
           tma_load_3d(base + OFF_K + st * KV_BYTES, &tmap_k, bar(K_FULL0 + st), 0, kvh, row);
           if constexpr (G::NSUB == 2) tma_load_3d(base + OFF_K + st * KV_BYTES + KV_SUB, &tmap_k, bar(K_FULL0 + st), 64, kvh, row);
           if (use > 0 && !(ok = wait_or_abort(bar(PV_DONE0 + st), (use - 1) & 1, abort_flag))) break;
-          // the previous item's epilogue stages O through both V stages
-          if (j < 2 && it > 0 && !(ok = wait_or_abort(bar(STAGE_FREE), (it - 1) & 1, abort_flag))) break;
           mbar_expect_tx(bar(V_FULL0 + st), KV_BYTES);
           tma_load_3d(base + OFF_V + st * KV_BYTES, &tmap_v, bar(V_FULL0 + st), 0, kvh, row);
           if constexpr (G::NSUB == 2) tma_load_3d(base + OFF_V + st * KV_BYTES + KV_SUB, &tmap_v, bar(V_FULL0 + st), 64, kvh, row);
@@ -278,14 +287,14 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
     // ------------------------------------------------------------------ softmax rows
     const int r = warp * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
-    unsigned char* stage = base_ptr + OFF_V;  // both V stages = one 32 KB O tile in bf16
+    unsigned char* stage = base_ptr + G::OFF_STAGE + warp * 2048;  // this warp's 32 rows x 64 B
     int T = 0;
     bool ok = true;
     for (int it = 0; ok; ++it) {
       if (!(ok = wait_or_abort(bar(ITEM_FULL0 + (it & 1)), (it >> 1) & 1, abort_flag))) break;
       const Item x = read_item(it);
       if (x.n_kv < 0) break;
-      const int qi = x.m0 + r, off = x.Lk - x.Lq;
+      const int qi = x.m0 + (r >> pl), off = x.Lk - x.Lq;
       float m_used = -INFINITY, l = 0.f;
       for (int j = 0; j < x.n_kv; ++j) {
         const int t = T + j, st = t & 1, ph = (t >> 1) & 1;
@@ -377,10 +386,14 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
       if (!ok) break;
       T += x.n_kv;
 
-      // epilogue: O / l -> bf16, staged through the V ring, stored as whole rows
+      // epilogue: O / l -> bf16; 32 columns at a time through this warp's patch of shared memory
       if (!(ok = wait_or_abort(bar(PV_DONE0 + ((T - 1) & 1)), ((T - 1) >> 1) & 1, abort_flag))) break;
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
+      // lane -> (row, 16-byte piece) of the eight 64-byte row segments one store instruction writes
+      const int srow = lane >> 2, spiece = lane & 3;
+      __nv_bfloat16* out_tile = p.out + static_cast<int64_t>(x.q0 + x.m0) * p.out_stride + x.h * D;
+      const int toks_valid = min(BMT, x.Lq - x.m0);
 #pragma unroll
       for (int c = 0; c < OCH; ++c) {
         uint32_t o[32];
@@ -398,25 +411,21 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
           v.y = pack_bf16x2(__uint_as_float(o[8 * k + 2]) * inv, __uint_as_float(o[8 * k + 3]) * inv);
           v.z = pack_bf16x2(__uint_as_float(o[8 * k + 4]) * inv, __uint_as_float(o[8 * k + 5]) * inv);
           v.w = pack_bf16x2(__uint_as_float(o[8 * k + 6]) * inv, __uint_as_float(o[8 * k + 7]) * inv);
-          const int cc = c * 4 + k;  // 16-byte piece of the row
-          *reinterpret_cast<uint4*>(stage + r * ROWB + ((cc ^ (r & (PIECES - 1))) << 4)) = v;
+          *reinterpret_cast<uint4*>(stage + lane * 64 + ((k ^ ((lane >> 1) & 3)) << 4)) = v;
         }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int lr = i * 8 + srow;       // row within the warp's 32
+          const int row = warp * 32 + lr;    // row of the tile
+          const int tok = row >> pl, hh = row & ((1 << pl) - 1);
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + lr * 64 + ((spiece ^ ((lr >> 1) & 3)) << 4));
+          if (tok < toks_valid)
+            *reinterpret_cast<uint4*>(out_tile + static_cast<int64_t>(tok) * p.out_stride + hh * D + c * 32 + spiece * 8) = v;
+        }
+        __syncwarp();
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four softmax warps only
-      __nv_bfloat16* out_tile = p.out + static_cast<int64_t>(x.q0 + x.m0) * p.out_stride + x.h * D;
-      const int rows_valid = min(BM, x.Lq - x.m0);
-#pragma unroll 4
-      for (int idx = r; idx < BM * PIECES; idx += 128) {
-        const int row = idx / PIECES, cc = idx % PIECES;
-        if (row < rows_valid)
-          *reinterpret_cast<uint4*>(out_tile + static_cast<int64_t>(row) * p.out_stride + cc * 8) =
-              *reinterpret_cast<const uint4*>(stage + row * ROWB + ((cc ^ (row & (PIECES - 1))) << 4));
-      }
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar(STAGE_FREE));
-        mbar_arrive(bar(ITEM_FREE0 + (it & 1)));
-      }
+      if (lane == 0) mbar_arrive(bar(ITEM_FREE0 + (it & 1)));
     }
   }
 
@@ -440,7 +449,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
 // ---- host side ---------------------------------------------------------------------------
 
 template <int D>
-static int launch_prefill_tcp_t(const PrefillParams& p, int64_t total_q, int64_t total_k, cudaStream_t stream) {
+static int launch_prefill_tcp_t(const PrefillParams& p_in, int64_t total_q, int64_t total_k, cudaStream_t stream) {
   using G = tcp::Geo<D>;
   static bool attr_done[64] = {false};
   static int num_sms[64] = {0};
@@ -454,8 +463,16 @@ static int launch_prefill_tcp_t(const PrefillParams& p, int64_t total_q, int64_t
     if (e != cudaSuccess) return fail(NVLLM_E_CUDA, "prefill (persistent): set-up failed: %s", cudaGetErrorString(e));
     attr_done[dev] = true;
   }
+  // heads packed into a query tile: the largest power of two that divides the group size, at most 8
+  // (NVLLM_PREFILL_PACK = 1 | 2 | 4 | 8 caps it; measurement aid, read on every call)
+  int cap = 8;
+  if (const char* s = std::getenv("NVLLM_PREFILL_PACK")) cap = std::atoi(s);
+  PrefillParams p = p_in;
+  p.pack_log2 = 0;
+  while (p.pack_log2 < 3 && (2 << p.pack_log2) <= cap && p.g % (2 << p.pack_log2) == 0) ++p.pack_log2;
+  const int pack = 1 << p.pack_log2, bmt = tc::BM >> p.pack_log2;
   CUtensorMap mq, mk, mv;
-  if (!make_tmap_3d(&mq, p.q, D, p.hq, total_q, D, p.q_stride, tc::BM)) return NVLLM_E_CUDA;
+  if (!make_tmap_3d(&mq, p.q, D, p.hq, total_q, D, p.q_stride, bmt, pack)) return NVLLM_E_CUDA;
   if (p.block_tables) {
     const uint64_t slots = static_cast<uint64_t>(p.num_blocks) * kBlockSize;
     const uint64_t row = static_cast<uint64_t>(p.hkv) * D;
@@ -466,7 +483,7 @@ static int launch_prefill_tcp_t(const PrefillParams& p, int64_t total_q, int64_t
     if (!make_tmap_3d(&mv, p.v, D, p.hkv, total_k, D, p.v_stride, tc::BN)) return NVLLM_E_CUDA;
   }
   // an upper bound of the work items known to the host: no more blocks than that
-  const int64_t max_items = static_cast<int64_t>((p.max_seqlen_q + tc::BM - 1) / tc::BM) * p.hq * p.batch;
+  const int64_t max_items = static_cast<int64_t>((p.max_seqlen_q + bmt - 1) / bmt) * (p.hq / pack) * p.batch;
   int grid = 2 * num_sms[dev];
   if (max_items < grid) grid = static_cast<int>(max_items);
   // the two head_dim instantiations share the counter array: give each its own half

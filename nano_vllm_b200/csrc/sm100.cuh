@@ -13,11 +13,12 @@ namespace sm100 {
 
 // ---- host: tensor maps -----------------------------------------------------------------
 
-// 3-D bf16 tensor map {inner = head_dim, heads, rows} with a {64, 1, box_rows} box and the
-// 128-byte swizzle that the UMMA descriptors below expect.  Returns false (message set) on
+// 3-D bf16 tensor map {inner = head_dim, heads, rows} with a {64, box_heads, box_rows} box (in
+// shared memory: 128-byte rows ordered row-major over (row, head)) and the 128-byte swizzle that
+// the UMMA descriptors below expect.  Returns false (message set) on
 // failure.  Pure host work; legal during stream capture.
 bool make_tmap_3d(CUtensorMap* map, const void* base, uint64_t head_dim, uint64_t heads, uint64_t rows,
-                  uint64_t head_stride_elems, uint64_t row_stride_elems, uint32_t box_rows);
+                  uint64_t head_stride_elems, uint64_t row_stride_elems, uint32_t box_rows, uint32_t box_heads = 1);
 
 #ifdef __CUDACC__
 

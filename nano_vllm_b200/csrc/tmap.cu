@@ -28,7 +28,7 @@ static EncodeTiledFn encoder() {
 }
 
 bool make_tmap_3d(CUtensorMap* map, const void* base, uint64_t head_dim, uint64_t heads, uint64_t rows,
-                  uint64_t head_stride_elems, uint64_t row_stride_elems, uint32_t box_rows) {
+                  uint64_t head_stride_elems, uint64_t row_stride_elems, uint32_t box_rows, uint32_t box_heads) {
   EncodeTiledFn enc = encoder();
   if (!enc) {
     fail(NVLLM_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
@@ -36,7 +36,7 @@ bool make_tmap_3d(CUtensorMap* map, const void* base, uint64_t head_dim, uint64_
   }
   const cuuint64_t dims[3] = {head_dim, heads, rows};
   const cuuint64_t strides[2] = {head_stride_elems * 2, row_stride_elems * 2};  // bytes, dims 1 and 2
-  const cuuint32_t box[3] = {64, 1, box_rows};
+  const cuuint32_t box[3] = {64, box_heads, box_rows};
   const cuuint32_t elem_strides[3] = {1, 1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem_strides,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
