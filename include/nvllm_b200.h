@@ -191,6 +191,25 @@ NVLLM_API int nvllm_qk_norm_rope_store(void* qkv, int64_t row_stride, const int6
                              int64_t n_tokens, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
                              void* stream);
 
+/*
+ * Token sampling in one pass over the logits [batch, vocab] (bf16, or fp32 when logits_are_fp32
+ * != 0; row stride in elements): tokens[b] = argmax_i(logits[b,i]) when temperatures[b] == 0,
+ * else a draw from softmax(logits[b] / temperatures[b]) made as
+ *     argmax_i( logits[b,i] / T_b - ln(e_i + 1e-10) ),   e_i ~ Exponential(1),
+ * which is the reference's argmax(softmax(logits / T) / (e + 1e-10)) without the normaliser.
+ * Replaces Sampler.forward (nanovllm/layers/sampler.py:10-26).  exponential_noise, when not
+ * NULL, is the caller's [batch, vocab] fp32 draw of e (then the result is the reference's token
+ * for the same draw); when NULL, e comes from a Philox4x32-10 generator keyed by `seed` and
+ * counted by (row, position, `step`): stateless, the same (seed, step) gives the same tokens,
+ * and the caller advances `step` once per call.  tokens is int64 [batch].  Ties go to the lowest
+ * index; NaN logits are never chosen.  Rows that start on a 16-byte boundary are read with
+ * 16-byte loads, others element by element (no alignment is required).
+ */
+NVLLM_API int nvllm_sample_tokens(const void* logits, int32_t logits_are_fp32, int64_t row_stride,
+                        const float* temperatures, const float* exponential_noise, int64_t noise_row_stride,
+                        uint64_t seed, uint64_t step, int64_t* tokens, int32_t batch, int32_t vocab,
+                        void* stream);
+
 /* Known-answer check of the tensor-core building blocks the prefill kernel is made of
  * (TMA swizzled loads, shared-memory and instruction descriptors, TMEM loads and stores):
  * out_ss = A B^T and out_ts = A B for A, B [128,128] bf16 row-major, outputs [128,128] fp32.

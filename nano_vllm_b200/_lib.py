@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_float, c_int32, c_int64, c_void_p, POINTER
+from ctypes import c_char_p, c_float, c_int32, c_int64, c_uint64, c_void_p, POINTER
 from pathlib import Path
 
 # NVLLM_B200_LIB points the loader at another build of the same library (e.g. one compiled
@@ -32,6 +32,8 @@ SIGNATURES = {
     "nvllm_qk_norm_rope_store": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float,
                                            c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int32, c_int32, c_int32,
                                            c_void_p]),
+    "nvllm_sample_tokens": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_uint64, c_uint64,
+                                      c_void_p, c_int32, c_int32, c_void_p]),
     "nvllm_selftest_umma": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvllm_selftest_wait_expiry": (c_int32, [c_void_p, c_void_p]),
     "nvllm_last_error": (c_char_p, []),

@@ -237,6 +237,33 @@ def qk_norm_rope_store(qkv: torch.Tensor, positions: torch.Tensor, q_weight: tor
             qkv.shape[0], num_q_heads, num_kv_heads, head_dim, _stream(qkv)))
 
 
+def sample_tokens(logits: torch.Tensor, temperatures: torch.Tensor, noise: torch.Tensor | None = None,
+                  seed: int = 0, step: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row of ``logits`` ``[B, V]`` (bf16 or fp32): argmax where the row's temperature
+    is 0, else a draw from ``softmax(logits / T)``.  One launch for what
+    nanovllm/layers/sampler.py:10-26 does in eight.  ``noise`` ``[B, V]`` fp32, when given, is the
+    Exponential(1) draw to use (the reference's ``torch.empty_like(probs).exponential_(1)``);
+    otherwise the kernel generates its own from ``(seed, step)``.  Returns int64 ``[B]``.
+    """
+    assert logits.is_cuda and logits.dim() == 2 and logits.stride(-1) == 1
+    assert logits.dtype in (torch.bfloat16, torch.float32), f"logits must be bf16 or fp32, got {logits.dtype}"
+    B, V = logits.shape
+    assert temperatures.is_cuda and temperatures.dtype == torch.float32 and temperatures.numel() == B
+    assert temperatures.is_contiguous()
+    if noise is not None:
+        assert noise.is_cuda and noise.dtype == torch.float32 and noise.shape == logits.shape and noise.stride(-1) == 1
+    if out is None:
+        out = torch.empty(B, dtype=torch.int64, device=logits.device)
+    else:
+        assert out.is_cuda and out.dtype == torch.int64 and out.numel() == B and out.is_contiguous()
+    with torch.cuda.device(logits.device):
+        _lib.check(_lib.load().nvllm_sample_tokens(
+            logits.data_ptr(), 1 if logits.dtype == torch.float32 else 0, logits.stride(0), temperatures.data_ptr(),
+            noise.data_ptr() if noise is not None else None, noise.stride(0) if noise is not None else 0,
+            seed & 0xFFFFFFFFFFFFFFFF, step & 0xFFFFFFFFFFFFFFFF, out.data_ptr(), B, V, _stream(logits)))
+    return out
+
+
 # ---- the layer --------------------------------------------------------------------------
 
 class Attention(nn.Module):

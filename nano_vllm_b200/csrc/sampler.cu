@@ -1,0 +1,208 @@
+// Token sampling in one pass over the logits.
+//
+// Stands where nano-vllm's Sampler.forward stands (nanovllm/layers/sampler.py:10-26), which
+// spends eight elementwise / reduction launches over a [batch, vocab] fp32 copy of the logits:
+//   greedy = argmax(logits);  probs = softmax(logits / T);
+//   sample = argmax(probs / (Exponential(1) + 1e-10));  token = (T == 0) ? greedy : sample.
+// argmax(p_i / e_i) is the Gumbel-max ("exponential race") way of drawing from p.  Since the
+// softmax normaliser and the row maximum are common to a row, the same token is
+//   argmax_i ( logit_i / T  -  ln(e_i + 1e-10) ),
+// which needs neither the maximum nor the sum: one read of the row, no intermediate tensor.
+//
+// Two noise sources.  (1) `noise` given: e_i is read from the caller's [batch, vocab] fp32
+// tensor; with the tensor the reference drew, the result is the reference's token (up to
+// rounding when two candidates tie to ~1e-6 relative).  (2) `noise` NULL: e_i = -ln(1 - v)
+// with v uniform in (0,1) from a Philox4x32-10 counter-based generator keyed by (seed) and
+// counted by (row, position in the row, step); no state is kept between calls, the same
+// (seed, step) reproduces the same tokens.
+//
+// One block per row, 1024 threads, 16-byte loads; ties go to the lowest index.
+#include "common.cuh"
+
+namespace nvllm {
+
+struct SampleParams {
+  const void* logits;
+  int64_t row_stride;
+  const float* temperatures;
+  const float* noise;  // nullable
+  int64_t noise_stride;
+  uint64_t seed, step;
+  int64_t* tokens;
+  int vocab;
+};
+
+// Philox4x32 with 10 rounds (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11).
+__device__ __forceinline__ uint4 philox4x32_10(uint4 ctr, uint2 key) {
+  constexpr uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint32_t hi0 = __umulhi(M0, ctr.x), lo0 = M0 * ctr.x;
+    const uint32_t hi1 = __umulhi(M1, ctr.z), lo1 = M1 * ctr.z;
+    ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+    key.x += W0;
+    key.y += W1;
+  }
+  return ctr;
+}
+
+// ln of an Exponential(1) draw made from 32 random bits.  v = (bits + 0.5) / 2^32 is uniform in
+// (0,1) and e = -ln(1 - v); for small v the series keeps the relative precision that 1 - v
+// would lose (small e decides which unlikely token wins, large e never matters).
+__device__ __forceinline__ float ln_exponential(uint32_t bits) {
+  const float v = (static_cast<float>(bits >> 8) + 0.5f) * 5.9604644775390625e-08f;  // 24 bits, never 0 or 1
+  float e;
+  if (v < 0.03125f) {
+    // the low 8 bits refine v where it is small enough for them to matter
+    const float vf = (static_cast<float>(bits) + 0.5f) * 2.3283064365386963e-10f;
+    e = vf * (1.f + vf * (0.5f + vf * (0.33333334f + vf * 0.25f)));
+  } else {
+    e = -__logf(1.f - v);
+  }
+  return __logf(e);
+}
+
+struct Best {
+  float score;
+  int idx;
+};
+__device__ __forceinline__ void take(Best& b, float s, int i) {
+  // NaN never wins; ties keep the lower index
+  if (s > b.score || (s == b.score && i < b.idx)) {
+    b.score = s;
+    b.idx = i;
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T x);
+template <>
+__device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T>
+__global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
+  constexpr int VEC = 16 / sizeof(T);  // elements per 16-byte load: 8 bf16 or 4 fp32
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const T* x = static_cast<const T*>(p.logits) + static_cast<int64_t>(row) * p.row_stride;
+  const float* nz = p.noise ? p.noise + static_cast<int64_t>(row) * p.noise_stride : nullptr;
+  const float t = p.temperatures[row];
+  const bool greedy = !(t > 0.f) && !(t < 0.f);  // T == 0 (or NaN): plain argmax, as torch.where(T == 0, ...)
+  const float inv_t = greedy ? 1.f : 1.f / t;
+  const uint2 key = make_uint2(static_cast<uint32_t>(p.seed), static_cast<uint32_t>(p.seed >> 32));
+
+  Best best{-INFINITY, 0x7fffffff};
+  // score of element i given its logit; `bits` only used by the generator path
+  auto score_of = [&](float logit, int i, uint32_t bits) {
+    float s = logit * inv_t;
+    if (!greedy) s -= nz ? __logf(nz[i] + 1e-10f) : ln_exponential(bits);
+    return s;
+  };
+
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+  const int n_vec = vec_ok ? p.vocab / VEC : 0;
+  auto consume = [&](const uint4& raw, int v) {
+    const T* e = reinterpret_cast<const T*>(&raw);
+    uint32_t bits[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (!greedy && !nz) {
+#pragma unroll
+      for (int h = 0; h < VEC / 4; ++h) {
+        // counter: (group of 4 positions, row, step lo, step hi) -- unique per element and call
+        const uint4 r = philox4x32_10(make_uint4(static_cast<uint32_t>(v * (VEC / 4) + h), static_cast<uint32_t>(row),
+                                                 static_cast<uint32_t>(p.step), static_cast<uint32_t>(p.step >> 32)),
+                                      key);
+        bits[4 * h] = r.x; bits[4 * h + 1] = r.y; bits[4 * h + 2] = r.z; bits[4 * h + 3] = r.w;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) take(best, score_of(to_f32<T>(e[k]), v * VEC + k, bits[k]), v * VEC + k);
+  };
+  // four 16-byte loads in flight per thread before any of them is used
+  constexpr int UNROLL = 4;
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+  int v = tid;
+  for (; v + (UNROLL - 1) * static_cast<int>(blockDim.x) < n_vec; v += UNROLL * blockDim.x) {
+    uint4 raw[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) raw[u] = xv[v + u * blockDim.x];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) consume(raw[u], v + u * blockDim.x);
+  }
+  for (; v < n_vec; v += blockDim.x) consume(xv[v], v);
+  // tail (and whole rows that are not 16-byte aligned): one element at a time, same counters
+  for (int i = n_vec * VEC + tid; i < p.vocab; i += blockDim.x) {
+    uint32_t b = 0;
+    if (!greedy && !nz) {
+      const uint4 r = philox4x32_10(make_uint4(static_cast<uint32_t>(i >> 2), static_cast<uint32_t>(row),
+                                               static_cast<uint32_t>(p.step), static_cast<uint32_t>(p.step >> 32)),
+                                    key);
+      const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+      b = w[i & 3];
+    }
+    take(best, score_of(to_f32<T>(x[i]), i, b), i);
+  }
+
+  // block argmax: shuffle inside a warp, shared memory across the 32 warps
+#pragma unroll
+  for (int sh = 16; sh > 0; sh >>= 1) {
+    const float s = __shfl_xor_sync(0xffffffffu, best.score, sh);
+    const int i = __shfl_xor_sync(0xffffffffu, best.idx, sh);
+    take(best, s, i);
+  }
+  __shared__ float w_score[32];
+  __shared__ int w_idx[32];
+  if ((tid & 31) == 0) {
+    w_score[tid >> 5] = best.score;
+    w_idx[tid >> 5] = best.idx;
+  }
+  __syncthreads();
+  if (tid < 32) {
+    const int nw = (blockDim.x + 31) >> 5;
+    best.score = tid < nw ? w_score[tid] : -INFINITY;
+    best.idx = tid < nw ? w_idx[tid] : 0x7fffffff;
+#pragma unroll
+    for (int sh = 16; sh > 0; sh >>= 1) {
+      const float s = __shfl_xor_sync(0xffffffffu, best.score, sh);
+      const int i = __shfl_xor_sync(0xffffffffu, best.idx, sh);
+      take(best, s, i);
+    }
+    // a row of NaN / -inf only: token 0, like an argmax over equal values
+    if (tid == 0) p.tokens[row] = best.idx == 0x7fffffff ? 0 : best.idx;
+  }
+}
+
+}  // namespace nvllm
+
+extern "C" int nvllm_sample_tokens(const void* logits, int32_t logits_are_fp32, int64_t row_stride,
+                                   const float* temperatures, const float* exponential_noise, int64_t noise_row_stride,
+                                   uint64_t seed, uint64_t step, int64_t* tokens, int32_t batch, int32_t vocab,
+                                   void* stream) {
+  using namespace nvllm;
+  if (batch < 0 || vocab <= 0) return fail(NVLLM_E_GEOMETRY, "sample_tokens: batch=%d vocab=%d invalid", batch, vocab);
+  if (batch == 0) return NVLLM_OK;
+  if (!logits || !temperatures || !tokens) return fail(NVLLM_E_NULL, "sample_tokens: NULL pointer argument");
+  if (row_stride < vocab || (exponential_noise && noise_row_stride < vocab))
+    return fail(NVLLM_E_GEOMETRY, "sample_tokens: a row stride is smaller than vocab");
+  const size_t esz = logits_are_fp32 ? 4 : 2;
+  if (reinterpret_cast<uintptr_t>(logits) % esz || reinterpret_cast<uintptr_t>(tokens) % 8 ||
+      reinterpret_cast<uintptr_t>(temperatures) % 4 || reinterpret_cast<uintptr_t>(exponential_noise) % 4)
+    return fail(NVLLM_E_ALIGN, "sample_tokens: a pointer is not aligned to its element size");
+  SampleParams p;
+  p.logits = logits;
+  p.row_stride = row_stride;
+  p.temperatures = temperatures;
+  p.noise = exponential_noise;
+  p.noise_stride = noise_row_stride;
+  p.seed = seed;
+  p.step = step;
+  p.tokens = tokens;
+  p.vocab = vocab;
+  // rows whose start is not 16-byte aligned take the element-wise path inside the kernel
+  const int threads = vocab >= 8192 ? 1024 : 256;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (logits_are_fp32) sample_kernel<float><<<batch, threads, 0, st>>>(p);
+  else sample_kernel<__nv_bfloat16><<<batch, threads, 0, st>>>(p);
+  count_launch();
+  return check_launch("sample_tokens launch");
+}

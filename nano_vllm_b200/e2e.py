@@ -1,6 +1,6 @@
 """End-to-end throughput of nano-vllm with the B200 attention layer plugged in.
 
-    python -m nano_vllm_b200.e2e [--attn b200|reference] [--tp N] [--model qwen3-0.6b|qwen3-8b]
+    python -m nano_vllm_b200.e2e [--attn b200|b200-fused|b200-full|reference] [--tp N] [--model qwen3-0.6b|qwen3-8b]
                                  [--num-seqs 256] [--ref-path baseline/_ref]
 
 Runs the reference engine UNMODIFIED (scheduler, block manager with prefix caching, model
@@ -79,11 +79,13 @@ def apply_shims(attn: str, ref_path: str):
         sys.path.insert(0, ref_path)
     if str(ROOT) not in sys.path:
         sys.path.insert(0, str(ROOT))
-    if attn in ("b200", "b200-fused"):
+    if attn in ("b200", "b200-fused", "b200-full"):
         from nano_vllm_b200 import plugin
         plugin.install()
-        if attn == "b200-fused":
+        if attn in ("b200-fused", "b200-full"):
             plugin.fuse_pre_attention()
+        if attn == "b200-full":
+            plugin.fuse_sampler()
     import nanovllm.engine.model_runner as mr
     mr.load_model = random_init
 
@@ -134,9 +136,9 @@ def make_engine(model_dir: str, attn: str, ref_path: str, **kwargs):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--attn", default="b200", choices=["b200", "b200-fused", "reference"],
+    ap.add_argument("--attn", default="b200", choices=["b200", "b200-fused", "b200-full", "reference"],
                     help="b200: swap the attention layer; b200-fused: also fuse q/k norm + rotary + store; "
-                         "reference: stock nano-vllm")
+                         "b200-full: also the one-pass sampler; reference: stock nano-vllm")
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--model", default="qwen3-0.6b", choices=sorted(GEOMETRY))
     ap.add_argument("--num-seqs", type=int, default=256)

@@ -47,6 +47,23 @@ def fuse_pre_attention() -> None:
     qwen2.Qwen2Attention.forward = _fused_attention_forward(False)
 
 
+def fuse_sampler(seed: int | None = None) -> None:
+    """Optional step: replace ``Sampler.forward`` (nanovllm/layers/sampler.py:10-26) by the
+    one-pass sampling kernel.  Greedy rows (temperature 0) give the reference's tokens; sampled
+    rows follow the same distribution but another random stream (Philox keyed by ``seed``,
+    default ``torch.initial_seed()``, counted by the number of calls), so they are not the
+    tokens the reference's ``exponential_`` stream would have picked."""
+    sampler = importlib.import_module("nanovllm.layers.sampler")
+    import torch
+    state = {"seed": torch.initial_seed() if seed is None else seed, "step": 0}
+
+    def forward(self, logits, temperatures):
+        state["step"] += 1
+        return _attention.sample_tokens(logits, temperatures, seed=state["seed"], step=state["step"])
+
+    sampler.Sampler.forward = forward
+
+
 def install() -> types.ModuleType:
     already = sys.modules.get(MODULE_NAME)
     if already is not None and getattr(already, "__nano_vllm_b200__", False):

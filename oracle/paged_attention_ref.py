@@ -149,3 +149,21 @@ def qk_norm_rope_ref(qkv, positions, q_weight, k_weight, cos_sin_cache, eps, hq,
         q, k = rms_norm_ref(q, q_weight, eps), rms_norm_ref(k, k_weight, eps)
     cos, sin = cos_sin_cache[positions].chunk(2, dim=-1)
     return apply_rotary_ref(q, cos, sin), apply_rotary_ref(k, cos, sin), v
+
+
+# ---- sampling (nanovllm/layers/sampler.py:10-26) ------------------------------------------
+
+def sampler_scores_ref(logits, temperatures, noise):
+    """Per-row scores whose argmax is the token: the fp32 logits for a greedy row
+    (temperature 0), softmax(logits / T) / (noise + 1e-10) for a sampled row, where ``noise``
+    is the row's Exponential(1) draw (sampler.py:15-25)."""
+    x = logits.to(torch.float32)
+    t = temperatures.to(torch.float32)
+    probs = torch.softmax(x / t.unsqueeze(1), dim=-1, dtype=torch.float32)
+    race = probs / (noise.to(torch.float32) + 1e-10)
+    return torch.where((t == 0).unsqueeze(1), x, race)
+
+
+def sampler_ref(logits, temperatures, noise):
+    """Tokens of Sampler.forward for a given exponential draw (sampler.py:26)."""
+    return sampler_scores_ref(logits, temperatures, noise).argmax(dim=-1)

@@ -60,3 +60,34 @@ def input_fingerprint(*tensors) -> str:
         if t is not None:
             h.update(t.contiguous().view(torch.uint8).numpy().tobytes())
     return h.hexdigest()
+
+
+# ---- sampler -------------------------------------------------------------------------------
+
+def sampler_cases():
+    """name -> (logits bf16 [B,V], temperatures fp32 [B], noise fp32 [B,V], tokens int64 [B]) as
+    recorded by make_sampler_golden.py from nano-vllm's own Sampler on the CPU.  The widest
+    case stores only its seeds; its logits and noise are drawn again here the way the
+    recording script drew them."""
+    from pathlib import Path
+    import numpy as np
+    z = np.load(Path(__file__).resolve().parent / "sampler.npz")
+    names = sorted({k.split(".")[0] for k in z.files})
+    out = {}
+    for name in names:
+        t = torch.from_numpy(z[f"{name}.temperatures"].copy())
+        tokens = torch.from_numpy(z[f"{name}.tokens"].copy())
+        batch = t.numel()
+        if f"{name}.logits" in z.files:
+            logits = torch.from_numpy(z[f"{name}.logits"].copy()).view(torch.bfloat16)
+            noise = torch.from_numpy(z[f"{name}.noise"].copy())
+        else:
+            vocab = 151936
+            g = torch.Generator().manual_seed(int(z[f"{name}.logits_seed"]))
+            logits = (torch.randn(batch, vocab, generator=g) * 3.0).to(torch.bfloat16)
+            state = torch.random.get_rng_state()
+            torch.manual_seed(int(z[f"{name}.noise_seed"]))
+            noise = torch.empty(batch, vocab, dtype=torch.float32).exponential_(1)
+            torch.random.set_rng_state(state)
+        out[name] = (logits, t, noise, tokens)
+    return out

@@ -59,3 +59,12 @@ def test_prefill_oracle_matches_reference(name):
     else:
         ref = R.prefill_ref(case.q, case.k, case.v, case.cu_seqlens_q, case.cu_seqlens_k, case.scale)
     assert_close_to_oracle(_bf16(gold["out"]), ref, name)
+
+
+@pytest.mark.parametrize("name", ["ragged_vocab", "small", "wide"])
+def test_sampler_oracle_matches_reference(name):
+    """Tokens that nano-vllm's own Sampler returned on the CPU for a recorded exponential draw."""
+    logits, temperatures, noise, tokens = C.sampler_cases()[name]
+    assert torch.equal(R.sampler_ref(logits, temperatures, noise), tokens)
+    greedy = temperatures == 0
+    assert greedy.any() and torch.equal(tokens[greedy], logits.float().argmax(-1)[greedy])
