@@ -59,7 +59,7 @@ def parse_args():
     ap.add_argument("--no-secondary", action="store_true", help="skip the store/prefill/long-context extras")
     ap.add_argument("--no-engine", action="store_true",
                     help="skip the end-to-end nano-vllm engine run (output tok/s) that follows at 1 GPU")
-    ap.add_argument("--kernel", default=None, choices=["prefill", "prefill_long", "prefill_d64", "store", "decode", "decode_long"],
+    ap.add_argument("--kernel", default=None, choices=["prefill", "prefill_long", "prefill_d64", "store", "decode", "decode_long", "sampler"],
                     help="time only this secondary kernel on one GPU and print its line (profiling aid)")
     ap.add_argument("--with-flash-attn", action="store_true",
                     help="with --kernel: also time the library kernels the reference calls (flash-attn, Triton "
@@ -473,6 +473,31 @@ def secondary(dev, hbm_peak_gbs, only=None, compare=False):
             res["flash_attn_decode_cfg4_b256"] = {"us": round(ms * 1e3, 1), "GB/s": round(nb / ms / 1e6, 1),
                                                   "frac_of_hbm_peak": round(nb / ms / 1e6 / hbm_peak_gbs, 3)}
         del c4, o
+    if only in (None, "sampler"):
+        # the engine's decode-step tail: one token per row of [256, 151936] bf16 logits, T = 0.6
+        lg = (torch.randn(256, 151936, device=dev) * 2).to(torch.bfloat16)
+        tt = torch.full((256,), 0.6, device=dev)
+        tok = torch.empty(256, dtype=torch.int64, device=dev)
+        nb = lg.numel() * 2 + 256 * 12
+        calls = [0]
+
+        def draw():
+            calls[0] += 1
+            A.sample_tokens(lg, tt, seed=1, step=calls[0], out=tok)
+        ms = med(draw)
+        res["sampler_b256_v151936_t0.6"] = {"us": round(ms * 1e3, 1), "GB/s": round(nb / ms / 1e6, 1),
+                                            "frac_of_hbm_peak": round(nb / ms / 1e6 / hbm_peak_gbs, 3)}
+        stock = ROOT / "baseline" / "_ref" / "nanovllm" / "layers" / "sampler.py"
+        if compare and stock.is_file():  # nano-vllm's own sampler module (plain torch), loaded by file
+            import importlib.util
+            spec = importlib.util.spec_from_file_location("_stock_sampler", stock)
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            stock_sampler = mod.Sampler()
+            with torch.inference_mode():
+                ms = med(lambda: stock_sampler(lg, tt))
+            res["stock_sampler_b256_v151936_t0.6"] = {"us": round(ms * 1e3, 1), "GB/s": round(nb / ms / 1e6, 1)}
+        del lg, tt, tok
     if only in (None, "decode_long"):
         c5 = W.cfg5_decode(1, dev, batch=256)
         B, Hq, Hkv, D = c5.geometry
@@ -493,13 +518,14 @@ def secondary(dev, hbm_peak_gbs, only=None, compare=False):
 
 def engine_run():
     """Output tok/s of the unmodified nano-vllm engine (installed under baseline/_ref) with the
-    B200 attention layer swapped in: the reference's own benchmark workload on random-init
+    B200 attention layer, the fused pre-attention step and the one-pass sampler swapped in: the
+    reference's own benchmark workload on random-init
     Qwen3-0.6B, 1 GPU (python -m nano_vllm_b200.e2e).  Runs as a child process with a time limit;
     any failure is reported as a string instead of a number."""
     if not (ROOT / "baseline" / "_ref" / "nanovllm").is_dir():
         return {"unavailable": "no nano-vllm install under baseline/_ref"}
     try:
-        proc = subprocess.run([sys.executable, "-m", "nano_vllm_b200.e2e", "--attn", "b200-fused"], cwd=str(ROOT),
+        proc = subprocess.run([sys.executable, "-m", "nano_vllm_b200.e2e", "--attn", "b200-full"], cwd=str(ROOT),
                               capture_output=True, text=True, timeout=420)
         for ln in reversed(proc.stdout.strip().splitlines()):
             if ln.startswith("{"):

@@ -79,7 +79,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
   constexpr int Q_BYTES = G::Q_BYTES, Q_SUB = G::Q_SUB, KV_BYTES = G::KV_BYTES, KV_SUB = G::KV_SUB;
   constexpr int OFF_Q = G::OFF_Q, OFF_K = G::OFF_K, OFF_V = G::OFF_V, OFF_CTRL = G::OFF_CTRL;
   constexpr int OFF_SLOTS = G::OFF_SLOTS, OFF_MISC = G::OFF_MISC, OFF_PREFIX = G::OFF_PREFIX;
-  constexpr int OCH = G::OCH, ROWB = G::ROWB, PIECES = G::PIECES;
+  constexpr int OCH = G::OCH, PIECES = G::PIECES;
   extern __shared__ unsigned char smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 

@@ -16,7 +16,13 @@
 // counted by (row, position in the row, step); no state is kept between calls, the same
 // (seed, step) reproduces the same tokens.
 //
-// One block per row, 1024 threads, 16-byte loads; ties go to the lowest index.
+// A row is read by one thread-block cluster of 1, 2, 4 or 8 blocks of 256 threads (the fewer
+// the rows, the more blocks each gets, so that a decode batch of any size spreads over the 148
+// SMs); 16-byte loads, four in flight per thread.  Each block reduces to one candidate, block 0
+// of the cluster collects the others' candidates from their shared memory.  Ties go to the
+// lowest index.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace nvllm {
@@ -73,6 +79,13 @@ __device__ __forceinline__ void take(Best& b, float s, int i) {
     b.idx = i;
   }
 }
+// Same for a thread's own elements, which it visits in rising index order.
+__device__ __forceinline__ void take_next(Best& b, float s, int i) {
+  if (s > b.score) {
+    b.score = s;
+    b.idx = i;
+  }
+}
 
 template <typename T>
 __device__ __forceinline__ float to_f32(T x);
@@ -81,10 +94,24 @@ __device__ __forceinline__ float to_f32<float>(float x) { return x; }
 template <>
 __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
 
+// Build-time shape (measurement aid): resident blocks per SM the register budget is held to, and
+// 16-byte loads in flight per thread.
+#ifndef NVLLM_SAMPLER_MINBLOCKS
+#define NVLLM_SAMPLER_MINBLOCKS 4
+#endif
+#ifndef NVLLM_SAMPLER_UNROLL
+#define NVLLM_SAMPLER_UNROLL 4
+#endif
+
 template <typename T>
-__global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
+__global__ void __launch_bounds__(256, NVLLM_SAMPLER_MINBLOCKS) sample_kernel(const SampleParams p) {
   constexpr int VEC = 16 / sizeof(T);  // elements per 16-byte load: 8 bf16 or 4 fp32
-  const int row = blockIdx.x, tid = threadIdx.x;
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int csize = static_cast<int>(cluster.num_blocks()), crank = static_cast<int>(cluster.block_rank());
+  const int row = blockIdx.x / csize;
+  const int tid = crank * blockDim.x + threadIdx.x;  // thread index within the row's cluster
+  const int nthreads = csize * blockDim.x;
   const T* x = static_cast<const T*>(p.logits) + static_cast<int64_t>(row) * p.row_stride;
   const float* nz = p.noise ? p.noise + static_cast<int64_t>(row) * p.noise_stride : nullptr;
   const float t = p.temperatures[row];
@@ -116,22 +143,22 @@ __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
       }
     }
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) take(best, score_of(to_f32<T>(e[k]), v * VEC + k, bits[k]), v * VEC + k);
+    for (int k = 0; k < VEC; ++k) take_next(best, score_of(to_f32<T>(e[k]), v * VEC + k, bits[k]), v * VEC + k);
   };
   // four 16-byte loads in flight per thread before any of them is used
-  constexpr int UNROLL = 4;
+  constexpr int UNROLL = NVLLM_SAMPLER_UNROLL;
   const uint4* xv = reinterpret_cast<const uint4*>(x);
   int v = tid;
-  for (; v + (UNROLL - 1) * static_cast<int>(blockDim.x) < n_vec; v += UNROLL * blockDim.x) {
+  for (; v + (UNROLL - 1) * nthreads < n_vec; v += UNROLL * nthreads) {
     uint4 raw[UNROLL];
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) raw[u] = xv[v + u * blockDim.x];
+    for (int u = 0; u < UNROLL; ++u) raw[u] = xv[v + u * nthreads];
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) consume(raw[u], v + u * blockDim.x);
+    for (int u = 0; u < UNROLL; ++u) consume(raw[u], v + u * nthreads);
   }
-  for (; v < n_vec; v += blockDim.x) consume(xv[v], v);
+  for (; v < n_vec; v += nthreads) consume(xv[v], v);
   // tail (and whole rows that are not 16-byte aligned): one element at a time, same counters
-  for (int i = n_vec * VEC + tid; i < p.vocab; i += blockDim.x) {
+  for (int i = n_vec * VEC + tid; i < p.vocab; i += nthreads) {
     uint32_t b = 0;
     if (!greedy && !nz) {
       const uint4 r = philox4x32_10(make_uint4(static_cast<uint32_t>(i >> 2), static_cast<uint32_t>(row),
@@ -140,36 +167,52 @@ __global__ void __launch_bounds__(1024) sample_kernel(const SampleParams p) {
       const uint32_t w[4] = {r.x, r.y, r.z, r.w};
       b = w[i & 3];
     }
-    take(best, score_of(to_f32<T>(x[i]), i, b), i);
+    take_next(best, score_of(to_f32<T>(x[i]), i, b), i);
   }
 
-  // block argmax: shuffle inside a warp, shared memory across the 32 warps
-#pragma unroll
-  for (int sh = 16; sh > 0; sh >>= 1) {
-    const float s = __shfl_xor_sync(0xffffffffu, best.score, sh);
-    const int i = __shfl_xor_sync(0xffffffffu, best.idx, sh);
-    take(best, s, i);
-  }
-  __shared__ float w_score[32];
-  __shared__ int w_idx[32];
-  if ((tid & 31) == 0) {
-    w_score[tid >> 5] = best.score;
-    w_idx[tid >> 5] = best.idx;
-  }
-  __syncthreads();
-  if (tid < 32) {
-    const int nw = (blockDim.x + 31) >> 5;
-    best.score = tid < nw ? w_score[tid] : -INFINITY;
-    best.idx = tid < nw ? w_idx[tid] : 0x7fffffff;
+  // block argmax: shuffle inside a warp, shared memory across the warps; then across the cluster
+  auto warp_reduce = [&]() {
 #pragma unroll
     for (int sh = 16; sh > 0; sh >>= 1) {
       const float s = __shfl_xor_sync(0xffffffffu, best.score, sh);
       const int i = __shfl_xor_sync(0xffffffffu, best.idx, sh);
       take(best, s, i);
     }
-    // a row of NaN / -inf only: token 0, like an argmax over equal values
-    if (tid == 0) p.tokens[row] = best.idx == 0x7fffffff ? 0 : best.idx;
+  };
+  warp_reduce();
+  __shared__ float w_score[8];
+  __shared__ int w_idx[8];
+  __shared__ float blk_score;
+  __shared__ int blk_idx;
+  const int lt = threadIdx.x;
+  if ((lt & 31) == 0) {
+    w_score[lt >> 5] = best.score;
+    w_idx[lt >> 5] = best.idx;
   }
+  __syncthreads();
+  if (lt < 32) {
+    const int nw = (blockDim.x + 31) >> 5;
+    best.score = lt < nw ? w_score[lt] : -INFINITY;
+    best.idx = lt < nw ? w_idx[lt] : 0x7fffffff;
+    warp_reduce();
+    if (lt == 0) {
+      blk_score = best.score;
+      blk_idx = best.idx;
+    }
+  }
+  cluster.sync();  // every block's candidate is in its shared memory
+  if (crank == 0 && lt < 32) {
+    best.score = -INFINITY;
+    best.idx = 0x7fffffff;
+    if (lt < csize) {
+      best.score = *cluster.map_shared_rank(&blk_score, lt);
+      best.idx = *cluster.map_shared_rank(&blk_idx, lt);
+    }
+    warp_reduce();
+    // a row of NaN / -inf only: token 0, like an argmax over equal values
+    if (lt == 0) p.tokens[row] = best.idx == 0x7fffffff ? 0 : best.idx;
+  }
+  cluster.sync();  // no block leaves while its shared memory may still be read
 }
 
 }  // namespace nvllm
@@ -198,11 +241,29 @@ extern "C" int nvllm_sample_tokens(const void* logits, int32_t logits_are_fp32, 
   p.step = step;
   p.tokens = tokens;
   p.vocab = vocab;
-  // rows whose start is not 16-byte aligned take the element-wise path inside the kernel
-  const int threads = vocab >= 8192 ? 1024 : 256;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (logits_are_fp32) sample_kernel<float><<<batch, threads, 0, st>>>(p);
-  else sample_kernel<__nv_bfloat16><<<batch, threads, 0, st>>>(p);
+  // rows whose start is not 16-byte aligned take the element-wise path inside the kernel.
+  // Blocks per row: as many (1, 2, 4, 8) as keep the grid within one resident wave of
+  // 148 SMs x 8 blocks, and no more than the row has work for.
+  int csize = 8;
+  while (csize > 1 && (static_cast<int64_t>(batch) * csize > kNumSMs * (NVLLM_SAMPLER_MINBLOCKS > 4 ? NVLLM_SAMPLER_MINBLOCKS : 8) || vocab < csize * 256 * 8)) csize >>= 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(batch) * csize, 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = csize;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = logits_are_fp32 ? cudaLaunchKernelEx(&cfg, sample_kernel<float>, p)
+                                  : cudaLaunchKernelEx(&cfg, sample_kernel<__nv_bfloat16>, p);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(NVLLM_E_CUDA, "sample_tokens launch: %s", cudaGetErrorString(e));
+  }
   count_launch();
   return check_launch("sample_tokens launch");
 }
