@@ -210,6 +210,26 @@ NVLLM_API int nvllm_sample_tokens(const void* logits, int32_t logits_are_fp32, i
                         uint64_t seed, uint64_t step, int64_t* tokens, int32_t batch, int32_t vocab,
                         void* stream);
 
+/*
+ * Decode-step inputs for a captured CUDA graph, in one launch.  `staged` is a device copy of
+ * one host staging block holding, at the given BYTE offsets: tokens int64[batch] (last token of
+ * each sequence), lens int32[batch] (sequence lengths, the new token included), offsets
+ * int32[batch+1] and the concatenated block tables int32[offsets[batch]].  The kernel fills rows
+ * [0, graph_batch) of the graph's static tensors: input_ids / positions (int64), slot_mapping /
+ * context_lens (int32) and block_tables (int32, table_width columns, row stride in elements):
+ * rows < batch from the staged data (slot = last block * 256 + position of the newest token in
+ * it; table padded with -1 up to used_width = the widest table of the batch, 0 beyond), rows >=
+ * batch all zero.  Replaces the per-step copies of ModelRunner.prepare_decode /
+ * prepare_block_tables (nanovllm/engine/model_runner.py:151-159, 218-249) and the clear-and-copy
+ * of the graph buffers in run_model (model_runner.py:271-282), with bit-identical buffers over
+ * the rows the graph reads.
+ */
+NVLLM_API int nvllm_decode_step_inputs(const void* staged, int64_t tokens_off, int64_t lens_off, int64_t offsets_off,
+                             int64_t blocks_off, int32_t batch, int32_t graph_batch, int32_t used_width,
+                             int32_t table_width, int64_t* input_ids, int64_t* positions,
+                             int32_t* slot_mapping, int32_t* context_lens, int32_t* block_tables,
+                             int64_t bt_row_stride, void* stream);
+
 /* Known-answer check of the tensor-core building blocks the prefill kernel is made of
  * (TMA swizzled loads, shared-memory and instruction descriptors, TMEM loads and stores):
  * out_ss = A B^T and out_ts = A B for A, B [128,128] bf16 row-major, outputs [128,128] fp32.

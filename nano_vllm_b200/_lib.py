@@ -34,6 +34,8 @@ SIGNATURES = {
                                            c_void_p]),
     "nvllm_sample_tokens": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_uint64, c_uint64,
                                       c_void_p, c_int32, c_int32, c_void_p]),
+    "nvllm_decode_step_inputs": (c_int32, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32,
+                                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "nvllm_selftest_umma": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvllm_selftest_wait_expiry": (c_int32, [c_void_p, c_void_p]),
     "nvllm_last_error": (c_char_p, []),

@@ -86,6 +86,7 @@ def apply_shims(attn: str, ref_path: str):
             plugin.fuse_pre_attention()
         if attn == "b200-full":
             plugin.fuse_sampler()
+            plugin.fuse_decode_inputs()
     import nanovllm.engine.model_runner as mr
     mr.load_model = random_init
 
@@ -138,7 +139,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--attn", default="b200", choices=["b200", "b200-fused", "b200-full", "reference"],
                     help="b200: swap the attention layer; b200-fused: also fuse q/k norm + rotary + store; "
-                         "b200-full: also the one-pass sampler; reference: stock nano-vllm")
+                         "b200-full: also the one-pass sampler and the one-launch decode inputs; reference: stock nano-vllm")
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--model", default="qwen3-0.6b", choices=sorted(GEOMETRY))
     ap.add_argument("--num-seqs", type=int, default=256)

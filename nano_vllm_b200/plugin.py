@@ -64,6 +64,42 @@ def fuse_sampler(seed: int | None = None) -> None:
     sampler.Sampler.forward = forward
 
 
+def fuse_decode_inputs() -> None:
+    """Optional step: decode steps that replay a CUDA graph get their inputs through one staged
+    copy and one launch (decode_inputs.DecodeInputStager) instead of ``prepare_decode`` /
+    ``prepare_sample`` and the clear-and-copy in ``run_model``
+    (nanovllm/engine/model_runner.py:218-258, 271-282).  Prefill steps, eager decode and batches
+    beyond the captured sizes go through the stock ``ModelRunner.run``."""
+    import torch
+    mr = importlib.import_module("nanovllm.engine.model_runner")
+    ctx = importlib.import_module("nanovllm.utils.context")
+    from .decode_inputs import DecodeInputStager
+    stock_run = mr.ModelRunner.run
+
+    def run(self, seqs, is_prefill):
+        graphs = getattr(self, "graphs", None)
+        if is_prefill or self.enforce_eager or not graphs or len(seqs) > self.graph_bs[-1]:
+            return stock_run(self, seqs, is_prefill)
+        gv = self.graph_vars
+        stager = getattr(self, "_nvllm_stager", None)
+        if stager is None:
+            rows, width = gv["block_tables"].shape
+            stager = self._nvllm_stager = DecodeInputStager(rows, width, gv["block_tables"].device)
+        bs = len(seqs)
+        graph_bs = next(x for x in self.graph_bs if x >= bs)
+        with torch.inference_mode():
+            temperatures = stager.stage(seqs, graph_bs, gv)
+            ctx.set_context(False, slot_mapping=gv["slot_mapping"][:bs], context_lens=gv["context_lens"][:bs],
+                            block_tables=gv["block_tables"][:bs])
+            graphs[graph_bs].replay()
+            logits = self.model.compute_logits(gv["outputs"][:bs])
+            token_ids = self.sampler(logits, temperatures).tolist() if self.rank == 0 else None
+        ctx.reset_context()
+        return token_ids
+
+    mr.ModelRunner.run = run
+
+
 def install() -> types.ModuleType:
     already = sys.modules.get(MODULE_NAME)
     if already is not None and getattr(already, "__nano_vllm_b200__", False):

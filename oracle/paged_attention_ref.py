@@ -167,3 +167,30 @@ def sampler_scores_ref(logits, temperatures, noise):
 def sampler_ref(logits, temperatures, noise):
     """Tokens of Sampler.forward for a given exponential draw (sampler.py:26)."""
     return sampler_scores_ref(logits, temperatures, noise).argmax(dim=-1)
+
+
+# ---- decode-step inputs (nanovllm/engine/model_runner.py:151-159, 218-249, 271-282) ---------
+
+def decode_inputs_ref(seqs, graph_bs, table_width, block_size=BLOCK_SIZE):
+    """Rows [0, graph_bs) of the graph's static input tensors after the reference has prepared a
+    decode step of ``seqs`` (objects with last_token, num_tokens, block_table) and refreshed the
+    buffers: cleared, then the first len(seqs) rows overwritten, the block tables as a
+    [bs, widest] tensor padded with -1."""
+    import numpy as np
+    n = len(seqs)
+    out = {"input_ids": np.zeros(graph_bs, np.int64), "positions": np.zeros(graph_bs, np.int64),
+           "slot_mapping": np.zeros(graph_bs, np.int32), "context_lens": np.zeros(graph_bs, np.int32),
+           "block_tables": np.zeros((graph_bs, table_width), np.int32)}
+    widest = max(len(s.block_table) for s in seqs)
+    for i, s in enumerate(seqs):
+        length = s.num_tokens
+        num_blocks = (length + block_size - 1) // block_size
+        last_block_tokens = length - (num_blocks - 1) * block_size
+        out["input_ids"][i] = s.last_token
+        out["positions"][i] = length
+        out["context_lens"][i] = length
+        out["slot_mapping"][i] = s.block_table[-1] * block_size + last_block_tokens - 1
+        row = list(s.block_table) + [-1] * (widest - len(s.block_table))
+        out["block_tables"][i, :widest] = row
+    assert n <= graph_bs
+    return out

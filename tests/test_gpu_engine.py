@@ -22,7 +22,7 @@ from nano_vllm_b200 import e2e, _lib
 os.chdir(tempfile.mkdtemp())
 e2e.GEOMETRY["tiny"] = dict(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                             head_dim=128, intermediate_size=512, tie_word_embeddings=True)
-llm = e2e.make_engine(e2e.write_model_dir("tiny"), "b200-fused", %(ref)r, enforce_eager=False, max_model_len=2048,
+llm = e2e.make_engine(e2e.write_model_dir("tiny"), %(attn)r, %(ref)r, enforce_eager=False, max_model_len=2048,
                       max_num_seqs=16, tensor_parallel_size=1)
 from nanovllm.sampling_params import SamplingParams
 random.seed(1)
@@ -34,18 +34,32 @@ second = llm.generate(prompts, sp, use_tqdm=False)   # full blocks of every prom
 same = sum(a == b for x, y in zip(first, second) for a, b in zip(x["token_ids"], y["token_ids"]))
 total = sum(len(x["token_ids"]) for x in first)
 print(json.dumps({"lens": [len(x["token_ids"]) for x in first + second], "same": same, "total": total,
+                  "tokens": [x["token_ids"] for x in first + second],
                   "cached_blocks": hits_before, "status": _lib.read_status(), "launches": _lib.launch_count()}))
 """
 
 
-def test_generate_with_graphs_and_prefix_cache():
-    code = SCRIPT % {"root": str(ROOT), "ref": str(REF)}
+def _run(attn):
+    code = SCRIPT % {"root": str(ROOT), "ref": str(REF), "attn": attn}
     proc = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, cwd=str(ROOT))
     assert proc.returncode == 0, proc.stderr[-3000:]
-    d = json.loads([ln for ln in proc.stdout.splitlines() if ln.startswith("{")][-1])
+    return json.loads([ln for ln in proc.stdout.splitlines() if ln.startswith("{")][-1])
+
+
+def test_generate_with_graphs_and_prefix_cache():
+    d = _run("b200-fused")
     assert d["lens"] == [40] * 10
     assert d["cached_blocks"] >= 8            # 1 + 2 + 1 + 4 full blocks of the first pass were hashed
     assert d["status"] == 0 and d["launches"] > 0
     # greedy decoding: the second pass (prefix read through block_tables) must reproduce the first
     # (packed prefill) up to rare bf16 near-ties in a random-weight model
     assert d["same"] >= 0.9 * d["total"], d
+
+
+def test_one_launch_decode_inputs_and_fused_sampler_change_no_greedy_token():
+    """With temperature 0 the engine is deterministic: staging the decode inputs through one copy
+    and one launch, and taking the argmax in the sampling kernel, must reproduce every token of
+    the run that uses the engine's own prepare_decode / run_model / Sampler."""
+    stock_path, fused_path = _run("b200-fused"), _run("b200-full")
+    assert fused_path["status"] == 0 and fused_path["lens"] == [40] * 10
+    assert fused_path["tokens"] == stock_path["tokens"]
