@@ -3,6 +3,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -44,6 +45,14 @@ int* status_word() {
 }
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* s = std::getenv("NVLLM_PDL");
+    return s && s[0] == '1';
+  }();
+  return on;
+}
 
 int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();

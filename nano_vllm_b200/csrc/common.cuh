@@ -22,6 +22,12 @@ int check_launch(const char* what);
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// True when NVLLM_PDL=1 (read once per process): the decode and combine kernels are launched with
+// programmatic stream serialization, so that their blocks are already resident when the
+// predecessor in the stream drains.  Off by default: it measured +0.3 % on a 0.8 ms decode
+// step and +1 % on a 0.12 ms one.
+bool pdl_enabled();
+
 constexpr int kBlockSize = NVLLM_BLOCK_SIZE;
 constexpr int kNumSMs = 148;
 
@@ -34,6 +40,17 @@ DecodePlan make_decode_plan(int batch, int max_blocks, int hq, int hkv, int d);
 
 // ---- device side -----------------------------------------------------------------------
 #ifdef __CUDACC__
+
+// Programmatic dependent launch.  Every kernel that may be launched with the attribute calls
+// pdl_prologue() as its first statement: it lets the next kernel in the stream start launching,
+// then blocks until the previous kernel has completed and its writes are visible.  Because every
+// block waits before it does anything else, completion stays transitive along the stream, and a
+// kernel launched without the attribute (or after a kernel that never signals) sees both
+// instructions as no-ops.
+__device__ __forceinline__ void pdl_prologue() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -82,6 +99,23 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
   return y;
+}
+
+// Launch with (or, when `pdl` is false, without) programmatic stream serialization.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 #endif  // __CUDACC__

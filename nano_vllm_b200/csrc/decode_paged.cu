@@ -81,6 +81,7 @@ __global__ void __launch_bounds__(C::NW * 32) decode_paged_kernel(const DecodePa
   constexpr int D = C::D, TT = C::TT, NST = C::NST, NW = C::NW;
   extern __shared__ __align__(128) unsigned char smem[];
 
+  pdl_prologue();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gid = lane >> 2, tig = lane & 3;
 
@@ -302,6 +303,7 @@ __global__ void __launch_bounds__(C::NW * 32) decode_paged_kernel(const DecodePa
 // Merges the split-KV partials of one (sequence, query head): grid = batch*hq, D threads.
 template <int D>
 __global__ void __launch_bounds__(D) decode_combine_kernel(const DecodeParams p) {
+  pdl_prologue();
   const int row = blockIdx.x;
   const int b = row / p.hq, head = row % p.hq;
   int ctx = p.ctx_lens[b];
@@ -384,16 +386,22 @@ static int launch_decode(const DecodeParams& p, cudaStream_t stream) {
   }
   const int64_t grid = static_cast<int64_t>(p.batch) * p.hkv * p.max_splits;
   if (grid > 0x7fffffffLL) return fail(NVLLM_E_GEOMETRY, "decode_paged: grid too large");
-  decode_paged_kernel<C><<<static_cast<unsigned>(grid), C::NW * 32, C::SMEM, stream>>>(p);
+  const bool pdl = pdl_enabled();
+  cudaError_t e = launch_kernel(decode_paged_kernel<C>, dim3(static_cast<unsigned>(grid)), dim3(C::NW * 32), C::SMEM, stream, pdl, p);
   count_launch();
-  int rc = check_launch("decode_paged launch");
-  if (rc) return rc;
-  if (p.max_splits > 1) {
-    decode_combine_kernel<C::D><<<p.batch * p.hq, C::D, 0, stream>>>(p);
-    count_launch();
-    rc = check_launch("decode_combine launch");
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(NVLLM_E_CUDA, "decode_paged launch: %s", cudaGetErrorString(e));
   }
-  return rc;
+  if (p.max_splits > 1) {
+    e = launch_kernel(decode_combine_kernel<C::D>, dim3(p.batch * p.hq), dim3(C::D), 0, stream, pdl, p);
+    count_launch();
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      return fail(NVLLM_E_CUDA, "decode_combine launch: %s", cudaGetErrorString(e));
+    }
+  }
+  return NVLLM_OK;
 }
 
 }  // namespace nvllm

@@ -41,6 +41,7 @@ struct PreAttnParams {
 
 template <int D>
 __global__ void __launch_bounds__(256) pre_attention_kernel(const PreAttnParams p) {
+  pdl_prologue();  // lets the attention kernel that follows get its blocks resident early
   constexpr int EPL = D / 64;  // elements per lane in each half of the head
   const int lane = threadIdx.x & 31;
   const int heads = p.hq + 2 * p.hkv;

@@ -15,6 +15,7 @@ store_kvcache_kernel(const uint4* __restrict__ key, int64_t key_stride16,      /
                      uint4* __restrict__ k_cache, uint4* __restrict__ v_cache,
                      const int32_t* __restrict__ slot_mapping,
                      int64_t n_tokens, int pieces_per_row, int64_t num_slots, int* __restrict__ status) {
+  pdl_prologue();  // lets the attention kernel that follows get its blocks resident early
   const int64_t total = n_tokens * pieces_per_row;
   const int64_t base = (static_cast<int64_t>(blockIdx.x) * kStoreThreads) * kStoreUnroll + threadIdx.x;
 
