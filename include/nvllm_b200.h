@@ -230,6 +230,40 @@ NVLLM_API int nvllm_decode_step_inputs(const void* staged, int64_t tokens_off, i
                              int32_t* slot_mapping, int32_t* context_lens, int32_t* block_tables,
                              int64_t bt_row_stride, void* stream);
 
+/*
+ * All-reduce (sum, bf16) over peer memory for tensor-parallel ranks on one node, one process per
+ * GPU.  Replaces dist.all_reduce in RowParallelLinear.forward (nanovllm/layers/linear.py:195-199)
+ * for tensors up to `max_bytes`.  Set-up, once per process and device, outside stream capture:
+ *   nvllm_ar_init(rank, world, max_bytes, handle_out)  allocates this rank's flag + staging area
+ *       (8 KB + 2 * max_bytes of device memory) and writes its CUDA IPC handle
+ *       (nvllm_ar_handle_bytes() bytes) to handle_out;
+ *   the caller gathers the handles of all ranks (rank order) by its own means;
+ *   nvllm_ar_connect(all_handles)  maps every peer's area.
+ * nvllm_ar_allreduce(in, out, n_elems, stream) then launches one kernel; every rank must make the
+ * same sequence of calls with the same n_elems.  in == out is allowed; both 16-byte aligned;
+ * n_elems * 2 <= max_bytes.  All ranks get bit-identical sums (fp32 accumulation in rank order).
+ * No allocation, synchronisation or host read in the call: legal during stream capture, and a
+ * captured graph can be replayed (call counts live in device memory).  A peer that does not
+ * arrive within ~1 s of SM clocks sets NVLLM_STATUS_TIMEOUT; that call's output is invalid and
+ * later calls no longer wait.  nvllm_ar_shutdown() unmaps and frees (synchronises the device).
+ */
+NVLLM_API int64_t nvllm_ar_handle_bytes(void);
+NVLLM_API int nvllm_ar_init(int32_t rank, int32_t world, int64_t max_bytes, void* handle_out);
+NVLLM_API int nvllm_ar_connect(const void* all_handles);
+NVLLM_API int64_t nvllm_ar_max_bytes(void); /* 0 until connected */
+NVLLM_API int nvllm_ar_allreduce(const void* in, void* out, int64_t n_elems, void* stream);
+NVLLM_API int nvllm_ar_shutdown(void);
+/* The same hand-shake and arithmetic with all `world` ranks emulated by ONE cooperative launch on
+ * the current device (inputs[r], outputs[r]: rank r's tensors; scratch: zero-filled before the
+ * first call, nvllm_ar_emulated_scratch_bytes(world, max_bytes) bytes, kept between calls).  For
+ * testing the protocol where fewer GPUs than ranks are at hand; absent_rank >= 0 makes that rank
+ * stay away, so that the others' bounded waits run out (~1 s) and report NVLLM_STATUS_TIMEOUT
+ * without any fault; -1 = all present.  No counterpart in the reference. */
+NVLLM_API int64_t nvllm_ar_emulated_scratch_bytes(int32_t world, int64_t max_bytes);
+NVLLM_API int nvllm_ar_allreduce_emulated(int32_t world, const void* const* inputs, void* const* outputs,
+                                int64_t n_elems, void* scratch, int64_t scratch_bytes, int64_t max_bytes,
+                                int32_t absent_rank, void* stream);
+
 /* Known-answer check of the tensor-core building blocks the prefill kernel is made of
  * (TMA swizzled loads, shared-memory and instruction descriptors, TMEM loads and stores):
  * out_ss = A B^T and out_ts = A B for A, B [128,128] bf16 row-major, outputs [128,128] fp32.

@@ -1,0 +1,70 @@
+"""All-reduce over peer memory for tensor-parallel ranks (one process per GPU, one node).
+
+Host side of ``nvllm_ar_*``: stands where ``dist.all_reduce(y)`` stands in
+``RowParallelLinear.forward`` (nanovllm/layers/linear.py:195-199).  ``torch.distributed`` is used
+once, to hand every rank's CUDA IPC handle to every other rank; the reduction itself is one
+kernel per rank that reads its peers' staging buffers over NVLink.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+def gather_handles(handle: bytes, rank: int, world: int, dist=None) -> bytes:
+    """Every rank's handle, concatenated in rank order (an object all-gather on the default
+    process group; works on any backend)."""
+    if dist is None:
+        import torch.distributed as dist
+    parts: list = [None] * world
+    dist.all_gather_object(parts, handle)
+    assert parts[rank] == handle and all(isinstance(p, bytes) and len(p) == len(handle) for p in parts)
+    return b"".join(parts)
+
+
+class PeerAllReduce:
+    """``all_reduce(x)`` sums a contiguous bf16 CUDA tensor over the ranks in place.  Every rank
+    must construct it at the same point and make the same calls."""
+
+    def __init__(self, rank: int, world: int, max_bytes: int = 8 << 20, dist=None):
+        lib = _lib.load()
+        n = lib.nvllm_ar_handle_bytes()
+        buf = ctypes.create_string_buffer(n)
+        _lib.check(lib.nvllm_ar_init(rank, world, max_bytes, buf))
+        handles = gather_handles(buf.raw, rank, world, dist)
+        _lib.check(lib.nvllm_ar_connect(handles))
+        self.rank, self.world, self.max_bytes = rank, world, max_bytes
+
+    def fits(self, x: torch.Tensor) -> bool:
+        return (x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.data_ptr() % 16 == 0
+                and (x.numel() * 2 + 15) // 16 * 16 <= self.max_bytes)
+
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        if not self.fits(x):
+            raise RuntimeError("PeerAllReduce.all_reduce: contiguous 16-byte-aligned bf16 CUDA tensor of at most "
+                               f"{self.max_bytes} bytes expected")
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.load().nvllm_ar_allreduce(x.data_ptr(), x.data_ptr(), x.numel(),
+                                                      torch.cuda.current_stream(x.device).cuda_stream))
+        return x
+
+    def close(self) -> None:
+        _lib.check(_lib.load().nvllm_ar_shutdown())
+
+
+def all_reduce_emulated(inputs: list[torch.Tensor], scratch: torch.Tensor, max_bytes: int,
+                        absent_rank: int = -1) -> list[torch.Tensor]:
+    """All ranks' reductions in one cooperative launch on one device (test aid): returns one
+    output per rank.  ``scratch``: uint8, zero-filled before its first use, kept between calls."""
+    world = len(inputs)
+    outs = [torch.empty_like(x) for x in inputs]
+    arr = ctypes.c_void_p * world
+    with torch.cuda.device(inputs[0].device):
+        _lib.check(_lib.load().nvllm_ar_allreduce_emulated(
+            world, arr(*[x.data_ptr() for x in inputs]), arr(*[o.data_ptr() for o in outs]), inputs[0].numel(),
+            scratch.data_ptr(), scratch.numel(), max_bytes, absent_rank,
+            torch.cuda.current_stream(inputs[0].device).cuda_stream))
+    return outs

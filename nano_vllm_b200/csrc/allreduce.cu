@@ -1,0 +1,348 @@
+// One-shot all-reduce (sum, bf16) over peer memory, for the row-parallel projections that follow
+// the attention layer.
+//
+// nano-vllm sums the partial outputs of o_proj and down_proj across tensor-parallel ranks with
+// dist.all_reduce (nanovllm/layers/linear.py:195-199): 2 x layers NCCL calls per decode step on a
+// [batch, hidden] bf16 tensor of 0.5-2 MiB, i.e. latency-bound.  Here every rank owns one device
+// allocation that all its peers map through CUDA IPC:
+//
+//     [ flags: kMaxBlocks x kMaxRanks u32 | epochs: kMaxBlocks u32 | staging 0 | staging 1 ]
+//
+// One call = one kernel on every rank, same grid everywhere.  Block b of rank r
+//   1. copies its slice of the input into r's staging buffer (e & 1), e = the block's call count,
+//   2. publishes e into flag (b, r) of every peer (st.release.sys through the peer mapping),
+//   3. waits until its own flags (b, p) have reached e for every peer p (ld.acquire.sys; bounded
+//      by a clock limit, after which the status word gets NVLLM_STATUS_TIMEOUT, a latch in the
+//      allocation makes later calls give up at once, and the block carries on without hanging),
+//   4. sums slice b of every rank's staging buffer in rank order, in fp32, and writes bf16.
+// Every rank adds the same numbers in the same order, so all ranks hold bit-identical results.
+// Two staging buffers used in turn need no closing barrier: a peer cannot reach call e+2 (which
+// overwrites buffer e & 1) before this rank has published e+1, which it does after reading.
+// All loads of peer memory are plain 16-byte loads issued by each block itself (no multicast
+// object, no TMA); flags and epochs live in device memory, so a captured graph replays correctly.
+#include <cooperative_groups.h>
+
+#include <cstring>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace nvllm {
+namespace ar {
+
+constexpr int kMaxRanks = 8;
+constexpr int kMaxBlocks = 128;
+constexpr int kThreads = 512;
+constexpr int64_t kFlagBytes = kMaxBlocks * kMaxRanks * 4;
+constexpr int64_t kEpochOff = kFlagBytes;                      // u32[kMaxBlocks]
+constexpr int64_t kBrokenOff = kEpochOff + kMaxBlocks * 4;     // u32 latch
+constexpr int64_t kHeaderBytes = 8192;
+static_assert(kBrokenOff + 4 <= kHeaderBytes, "header");
+
+struct Peers {
+  unsigned char* base[kMaxRanks];
+};
+
+struct Params {
+  const uint4* in;
+  uint4* out;
+  int64_t n16;        // 16-byte vectors (8 bf16 each)
+  int64_t tail_elems; // elements after the last whole vector (handled by block 0)
+  int64_t stage_bytes;
+  int rank, world;
+  Peers peers;
+  int* status;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_volatile16(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void add8(float (&acc)[8], const uint4& v) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    acc[2 * i] += f.x;
+    acc[2 * i + 1] += f.y;
+  }
+}
+
+// The work of block `b` (of `nblocks`) on behalf of rank `rank`.
+__device__ void allreduce_block(const Params& p, int rank, int b, int nblocks) {
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_abort;
+  const int tid = threadIdx.x;
+  unsigned char* own = p.peers.base[rank];
+  uint32_t* epochs = reinterpret_cast<uint32_t*>(own + kEpochOff);
+  uint32_t* broken = reinterpret_cast<uint32_t*>(own + kBrokenOff);
+  if (tid == 0) {
+    s_epoch = epochs[b] + 1;
+    s_abort = *reinterpret_cast<volatile uint32_t*>(broken) != 0;
+  }
+  __syncthreads();
+  const uint32_t e = s_epoch;
+  const int64_t stage_off = kHeaderBytes + static_cast<int64_t>(e & 1) * p.stage_bytes;
+  const int64_t v0 = p.n16 * b / nblocks, v1 = p.n16 * (b + 1) / nblocks;
+  const bool has_tail = b == 0 && p.tail_elems > 0;
+
+  // 1. own slice -> own staging buffer
+  uint4* stage = reinterpret_cast<uint4*>(own + stage_off);
+  for (int64_t v = v0 + tid; v < v1; v += blockDim.x) stage[v] = p.in[v];
+  if (has_tail && tid < p.tail_elems) {
+    const __nv_bfloat16* in_t = reinterpret_cast<const __nv_bfloat16*>(p.in + p.n16);
+    reinterpret_cast<__nv_bfloat16*>(stage + p.n16)[tid] = in_t[tid];
+  }
+  __threadfence_system();
+  __syncthreads();
+
+  // 2. publish, 3. wait (one thread per peer)
+  if (tid < p.world && tid != rank) {
+    uint32_t* theirs = reinterpret_cast<uint32_t*>(p.peers.base[tid]) + b * kMaxRanks + rank;
+    st_release_sys(theirs, e);
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(own) + b * kMaxRanks + tid;
+    if (!s_abort) {
+      const long long t0 = clock64();
+      while (static_cast<int32_t>(ld_acquire_sys(mine) - e) < 0) {
+        if (clock64() - t0 > sm100::kWaitLimitCycles) {
+          atomicOr(p.status, NVLLM_STATUS_TIMEOUT);
+          *reinterpret_cast<volatile uint32_t*>(broken) = 1;  // later calls do not wait again
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  // 4. sum in rank order
+  for (int64_t v = v0 + tid; v < v1; v += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < p.world; ++r) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.peers.base[r] + stage_off);
+      add8(acc, ld_volatile16(src + v));
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    p.out[v] = o;
+  }
+  if (has_tail && tid < p.tail_elems) {
+    float acc = 0.f;
+    for (int r = 0; r < p.world; ++r) {
+      const volatile __nv_bfloat16_raw* src =
+          reinterpret_cast<const volatile __nv_bfloat16_raw*>(p.peers.base[r] + stage_off + p.n16 * 16);
+      __nv_bfloat16_raw raw;
+      raw.x = src[tid].x;
+      acc += __bfloat162float(__nv_bfloat16(raw));
+    }
+    reinterpret_cast<__nv_bfloat16*>(p.out + p.n16)[tid] = __float2bfloat16(acc);
+  }
+  if (tid == 0) epochs[b] = e;
+}
+
+__global__ void __launch_bounds__(kThreads) allreduce_kernel(const Params p) {
+  allreduce_block(p, p.rank, blockIdx.x, gridDim.x);
+}
+
+// All ranks in ONE launch on one device (blockIdx.y = rank; in/out per rank): the only legal way
+// to run the hand-shake with fewer GPUs than ranks, since blocks that wait on each other must be
+// resident together (cooperative launch).
+struct EmuParams {
+  Params base;
+  const uint4* in[kMaxRanks];
+  uint4* out[kMaxRanks];
+  int absent_rank;  // this rank's blocks leave at once (a peer that never arrives); -1 = none
+};
+__global__ void __launch_bounds__(kThreads) allreduce_emulated_kernel(const EmuParams ep) {
+  Params p = ep.base;
+  const int rank = blockIdx.y;
+  if (rank == ep.absent_rank) return;
+  p.in = ep.in[rank];
+  p.out = ep.out[rank];
+  allreduce_block(p, rank, blockIdx.x, gridDim.x);
+}
+
+// ---- host state (one per device of this process) ---------------------------------------------
+struct State {
+  bool ready = false, connected = false;
+  int rank = 0, world = 0;
+  int64_t stage_bytes = 0;
+  unsigned char* own = nullptr;
+  Peers peers{};
+};
+static State g_state[64];
+
+static State* current_state() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  return &g_state[dev];
+}
+
+// Every call uses the same grid, whatever the size: the blocks' call counts then advance in
+// lock-step, so all blocks of a call use the same staging buffer and the two-buffer argument
+// above holds for the whole tensor (a block whose slice is empty still takes part in the
+// hand-shake).
+constexpr int kGrid = 64;
+constexpr int kEmulatedGrid = 16;  // x ranks blocks must be resident together on one device
+static_assert(kGrid <= kMaxBlocks, "flag slots");
+
+}  // namespace ar
+}  // namespace nvllm
+
+using namespace nvllm;
+
+extern "C" int64_t nvllm_ar_handle_bytes(void) { return static_cast<int64_t>(sizeof(cudaIpcMemHandle_t)); }
+
+extern "C" int nvllm_ar_init(int32_t rank, int32_t world, int64_t max_bytes, void* handle_out) {
+  ar::State* s = ar::current_state();
+  if (!s) return fail(NVLLM_E_NO_DEVICE, "ar_init: no CUDA device is usable");
+  if (s->ready) return fail(NVLLM_E_GEOMETRY, "ar_init: already initialised on this device (call nvllm_ar_shutdown first)");
+  if (world < 2 || world > ar::kMaxRanks || rank < 0 || rank >= world)
+    return fail(NVLLM_E_GEOMETRY, "ar_init: rank=%d world=%d invalid (2..%d ranks)", rank, world, ar::kMaxRanks);
+  if (max_bytes <= 0 || max_bytes % 16) return fail(NVLLM_E_GEOMETRY, "ar_init: max_bytes must be a positive multiple of 16");
+  if (!handle_out) return fail(NVLLM_E_NULL, "ar_init: NULL handle_out");
+  const size_t total = static_cast<size_t>(ar::kHeaderBytes + 2 * max_bytes);
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, total);
+  if (e == cudaSuccess) e = cudaMemset(p, 0, total);
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    if (p) cudaFree(p);
+    return fail(NVLLM_E_CUDA, "ar_init: %s", cudaGetErrorString(e));
+  }
+  std::memcpy(handle_out, &h, sizeof(h));
+  s->ready = true;
+  s->connected = false;
+  s->rank = rank;
+  s->world = world;
+  s->stage_bytes = max_bytes;
+  s->own = static_cast<unsigned char*>(p);
+  for (int r = 0; r < ar::kMaxRanks; ++r) s->peers.base[r] = nullptr;
+  s->peers.base[rank] = s->own;
+  return NVLLM_OK;
+}
+
+extern "C" int nvllm_ar_connect(const void* all_handles) {
+  ar::State* s = ar::current_state();
+  if (!s || !s->ready) return fail(NVLLM_E_GEOMETRY, "ar_connect: nvllm_ar_init has not run on this device");
+  if (!all_handles) return fail(NVLLM_E_NULL, "ar_connect: NULL handles");
+  if (s->connected) return NVLLM_OK;
+  const unsigned char* hs = static_cast<const unsigned char*>(all_handles);
+  for (int r = 0; r < s->world; ++r) {
+    if (r == s->rank) continue;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, hs + static_cast<size_t>(r) * sizeof(h), sizeof(h));
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      return fail(NVLLM_E_CUDA, "ar_connect: cannot map rank %d's buffer: %s", r, cudaGetErrorString(e));
+    }
+    s->peers.base[r] = static_cast<unsigned char*>(p);
+  }
+  s->connected = true;
+  return NVLLM_OK;
+}
+
+extern "C" int nvllm_ar_shutdown(void) {
+  ar::State* s = ar::current_state();
+  if (!s || !s->ready) return NVLLM_OK;
+  cudaDeviceSynchronize();
+  for (int r = 0; r < s->world; ++r)
+    if (r != s->rank && s->peers.base[r]) cudaIpcCloseMemHandle(s->peers.base[r]);
+  cudaFree(s->own);
+  (void)cudaGetLastError();
+  *s = ar::State{};
+  return NVLLM_OK;
+}
+
+extern "C" int64_t nvllm_ar_max_bytes(void) {
+  ar::State* s = ar::current_state();
+  return (s && s->connected) ? s->stage_bytes : 0;
+}
+
+extern "C" int nvllm_ar_allreduce(const void* in, void* out, int64_t n_elems, void* stream) {
+  ar::State* s = ar::current_state();
+  if (!s || !s->connected) return fail(NVLLM_E_GEOMETRY, "ar_allreduce: not connected (nvllm_ar_init + nvllm_ar_connect first)");
+  if (n_elems < 0) return fail(NVLLM_E_GEOMETRY, "ar_allreduce: negative size");
+  if (n_elems == 0) return NVLLM_OK;
+  if (!in || !out) return fail(NVLLM_E_NULL, "ar_allreduce: NULL pointer argument");
+  if (!aligned16(in) || !aligned16(out)) return fail(NVLLM_E_ALIGN, "ar_allreduce: in/out must be 16-byte aligned");
+  if ((n_elems * 2 + 15) / 16 * 16 > s->stage_bytes)
+    return fail(NVLLM_E_WORKSPACE, "ar_allreduce: %lld bytes exceed the %lld-byte staging buffers", (long long)(n_elems * 2),
+                (long long)s->stage_bytes);
+  ar::Params p;
+  p.in = static_cast<const uint4*>(in);
+  p.out = static_cast<uint4*>(out);
+  p.n16 = n_elems / 8;
+  p.tail_elems = n_elems % 8;
+  p.stage_bytes = s->stage_bytes;
+  p.rank = s->rank;
+  p.world = s->world;
+  p.peers = s->peers;
+  p.status = status_word();
+  if (!p.status) return fail(NVLLM_E_NO_DEVICE, "ar_allreduce: no CUDA device is usable");
+  ar::allreduce_kernel<<<ar::kGrid, ar::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  count_launch();
+  return check_launch("ar_allreduce launch");
+}
+
+extern "C" int64_t nvllm_ar_emulated_scratch_bytes(int32_t world, int64_t max_bytes) {
+  return static_cast<int64_t>(world) * (ar::kHeaderBytes + 2 * max_bytes);
+}
+
+extern "C" int nvllm_ar_allreduce_emulated(int32_t world, const void* const* inputs, void* const* outputs, int64_t n_elems,
+                                           void* scratch, int64_t scratch_bytes, int64_t max_bytes, int32_t absent_rank,
+                                           void* stream) {
+  if (world < 2 || world > ar::kMaxRanks) return fail(NVLLM_E_GEOMETRY, "ar_allreduce_emulated: world=%d invalid", world);
+  if (!inputs || !outputs || !scratch) return fail(NVLLM_E_NULL, "ar_allreduce_emulated: NULL pointer argument");
+  if (max_bytes <= 0 || max_bytes % 16 || n_elems <= 0 || (n_elems * 2 + 15) / 16 * 16 > max_bytes)
+    return fail(NVLLM_E_GEOMETRY, "ar_allreduce_emulated: sizes invalid");
+  if (scratch_bytes < nvllm_ar_emulated_scratch_bytes(world, max_bytes) || !aligned16(scratch))
+    return fail(NVLLM_E_WORKSPACE, "ar_allreduce_emulated: scratch too small or misaligned");
+  ar::EmuParams ep;
+  ep.base.n16 = n_elems / 8;
+  ep.base.tail_elems = n_elems % 8;
+  ep.base.stage_bytes = max_bytes;
+  ep.base.rank = 0;
+  ep.base.world = world;
+  ep.base.status = status_word();
+  ep.base.in = nullptr;
+  ep.base.out = nullptr;
+  ep.absent_rank = absent_rank;
+  if (!ep.base.status) return fail(NVLLM_E_NO_DEVICE, "ar_allreduce_emulated: no CUDA device is usable");
+  for (int r = 0; r < ar::kMaxRanks; ++r) {
+    ep.base.peers.base[r] = r < world ? static_cast<unsigned char*>(scratch) + r * (ar::kHeaderBytes + 2 * max_bytes) : nullptr;
+    ep.in[r] = r < world ? static_cast<const uint4*>(inputs[r]) : nullptr;
+    ep.out[r] = r < world ? static_cast<uint4*>(outputs[r]) : nullptr;
+    if (r < world && (!aligned16(inputs[r]) || !aligned16(outputs[r])))
+      return fail(NVLLM_E_ALIGN, "ar_allreduce_emulated: in/out must be 16-byte aligned");
+  }
+  // few blocks per rank so that world x blocks fit on the device at once; cooperative launch
+  // refuses to start otherwise, instead of letting waiting blocks starve the ones they wait for
+  void* args[] = {&ep};
+  cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(ar::allreduce_emulated_kernel), dim3(ar::kEmulatedGrid, world),
+                                              dim3(ar::kThreads), args, 0, static_cast<cudaStream_t>(stream));
+  count_launch();
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(NVLLM_E_CUDA, "ar_allreduce_emulated launch: %s", cudaGetErrorString(e));
+  }
+  return NVLLM_OK;
+}

@@ -194,3 +194,13 @@ def decode_inputs_ref(seqs, graph_bs, table_width, block_size=BLOCK_SIZE):
         out["block_tables"][i, :widest] = row
     assert n <= graph_bs
     return out
+
+
+# ---- tensor-parallel sum (nanovllm/layers/linear.py:195-199) --------------------------------
+
+def allreduce_ref(inputs):
+    """Sum of the ranks' bf16 tensors: fp32 accumulation in rank order, rounded to bf16 once."""
+    acc = torch.zeros(inputs[0].shape, dtype=torch.float32)
+    for x in inputs:
+        acc += x.to(torch.float32)
+    return acc.to(torch.bfloat16)

@@ -67,3 +67,39 @@ def test_head_sharded_ranks_reassemble_the_unsharded_result():
         p.join(100)
         assert p.exitcode == 0
     assert result.get(timeout=5) is True
+
+
+def _handle_worker(rank, world, port, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nano_vllm_b200 import allreduce as AR
+        from oracle import paged_attention_ref as R
+        mine = bytes([rank + 1]) * 64                       # stands for this rank's IPC handle
+        every = AR.gather_handles(mine, rank, world, dist)
+        ok = every == b"".join(bytes([r + 1]) * 64 for r in range(world))
+        # the sum the peer-memory kernel must reproduce: the collective it replaces, on the same data
+        xs = [(torch.randn(1000, generator=torch.Generator().manual_seed(r)) * 2).to(torch.bfloat16) for r in range(world)]
+        y = xs[rank].to(torch.float32)
+        dist.all_reduce(y)
+        ok = ok and torch.equal(y.to(torch.bfloat16), R.allreduce_ref(xs))
+        result.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(120)
+def test_ranks_exchange_handles_in_rank_order_and_agree_on_the_sum():
+    """Host side of the peer-memory all-reduce, world_size 2 over gloo: every rank ends up with
+    all handles in rank order, and the oracle's sum equals the collective it stands in for."""
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_handle_worker, args=(r, 2, port, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(100)
+        assert p.exitcode == 0
+    got = dict(result.get(timeout=5) for _ in range(2))
+    assert got == {0: True, 1: True}
