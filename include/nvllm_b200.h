@@ -251,6 +251,9 @@ NVLLM_API int64_t nvllm_ar_handle_bytes(void);
 NVLLM_API int nvllm_ar_init(int32_t rank, int32_t world, int64_t max_bytes, void* handle_out);
 NVLLM_API int nvllm_ar_connect(const void* all_handles);
 NVLLM_API int64_t nvllm_ar_max_bytes(void); /* 0 until connected */
+/* How long a rank waits for its peers before it gives up (default ~1000 ms of SM clocks).  Ranks
+ * that run loosely coupled (one may be seconds behind while it compiles or captures) need more. */
+NVLLM_API int nvllm_ar_set_wait_ms(int64_t ms);
 NVLLM_API int nvllm_ar_allreduce(const void* in, void* out, int64_t n_elems, void* stream);
 NVLLM_API int nvllm_ar_shutdown(void);
 /* The same hand-shake and arithmetic with all `world` ranks emulated by ONE cooperative launch on

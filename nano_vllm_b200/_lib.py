@@ -40,6 +40,7 @@ SIGNATURES = {
     "nvllm_ar_init": (c_int32, [c_int32, c_int32, c_int64, c_void_p]),
     "nvllm_ar_connect": (c_int32, [c_void_p]),
     "nvllm_ar_max_bytes": (c_int64, []),
+    "nvllm_ar_set_wait_ms": (c_int32, [c_int64]),
     "nvllm_ar_allreduce": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p]),
     "nvllm_ar_shutdown": (c_int32, []),
     "nvllm_ar_emulated_scratch_bytes": (c_int64, [c_int32, c_int64]),

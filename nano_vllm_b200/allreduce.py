@@ -29,13 +29,15 @@ class PeerAllReduce:
     """``all_reduce(x)`` sums a contiguous bf16 CUDA tensor over the ranks in place.  Every rank
     must construct it at the same point and make the same calls."""
 
-    def __init__(self, rank: int, world: int, max_bytes: int = 8 << 20, dist=None):
+    def __init__(self, rank: int, world: int, max_bytes: int = 8 << 20, dist=None, wait_ms: int | None = None):
         lib = _lib.load()
         n = lib.nvllm_ar_handle_bytes()
         buf = ctypes.create_string_buffer(n)
         _lib.check(lib.nvllm_ar_init(rank, world, max_bytes, buf))
         handles = gather_handles(buf.raw, rank, world, dist)
         _lib.check(lib.nvllm_ar_connect(handles))
+        if wait_ms is not None:
+            _lib.check(lib.nvllm_ar_set_wait_ms(wait_ms))
         self.rank, self.world, self.max_bytes = rank, world, max_bytes
 
     def fits(self, x: torch.Tensor) -> bool:

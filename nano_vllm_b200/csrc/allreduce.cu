@@ -49,6 +49,7 @@ struct Params {
   int64_t n16;        // 16-byte vectors (8 bf16 each)
   int64_t tail_elems; // elements after the last whole vector (handled by block 0)
   int64_t stage_bytes;
+  long long wait_cycles;  // a wait for a peer gives up after this many SM clocks
   int rank, world;
   Peers peers;
   int* status;
@@ -113,7 +114,7 @@ __device__ void allreduce_block(const Params& p, int rank, int b, int nblocks) {
     if (!s_abort) {
       const long long t0 = clock64();
       while (static_cast<int32_t>(ld_acquire_sys(mine) - e) < 0) {
-        if (clock64() - t0 > sm100::kWaitLimitCycles) {
+        if (clock64() - t0 > p.wait_cycles) {
           atomicOr(p.status, NVLLM_STATUS_TIMEOUT);
           *reinterpret_cast<volatile uint32_t*>(broken) = 1;  // later calls do not wait again
           break;
@@ -178,6 +179,7 @@ struct State {
   bool ready = false, connected = false;
   int rank = 0, world = 0;
   int64_t stage_bytes = 0;
+  long long wait_cycles = sm100::kWaitLimitCycles;
   unsigned char* own = nullptr;
   Peers peers{};
 };
@@ -272,6 +274,14 @@ extern "C" int nvllm_ar_shutdown(void) {
   return NVLLM_OK;
 }
 
+extern "C" int nvllm_ar_set_wait_ms(int64_t ms) {
+  ar::State* s = ar::current_state();
+  if (!s || !s->ready) return fail(NVLLM_E_GEOMETRY, "ar_set_wait_ms: nvllm_ar_init has not run on this device");
+  if (ms < 1 || ms > 600000) return fail(NVLLM_E_GEOMETRY, "ar_set_wait_ms: %lld ms outside 1..600000", (long long)ms);
+  s->wait_cycles = ms * 2000000ll;  // SM clocks at ~2 GHz
+  return NVLLM_OK;
+}
+
 extern "C" int64_t nvllm_ar_max_bytes(void) {
   ar::State* s = ar::current_state();
   return (s && s->connected) ? s->stage_bytes : 0;
@@ -293,6 +303,7 @@ extern "C" int nvllm_ar_allreduce(const void* in, void* out, int64_t n_elems, vo
   p.n16 = n_elems / 8;
   p.tail_elems = n_elems % 8;
   p.stage_bytes = s->stage_bytes;
+  p.wait_cycles = s->wait_cycles;
   p.rank = s->rank;
   p.world = s->world;
   p.peers = s->peers;
@@ -320,6 +331,7 @@ extern "C" int nvllm_ar_allreduce_emulated(int32_t world, const void* const* inp
   ep.base.n16 = n_elems / 8;
   ep.base.tail_elems = n_elems % 8;
   ep.base.stage_bytes = max_bytes;
+  ep.base.wait_cycles = sm100::kWaitLimitCycles;
   ep.base.rank = 0;
   ep.base.world = world;
   ep.base.status = status_word();
