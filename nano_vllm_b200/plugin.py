@@ -88,7 +88,7 @@ def fuse_decode_inputs() -> None:
         bs = len(seqs)
         graph_bs = next(x for x in self.graph_bs if x >= bs)
         with torch.inference_mode():
-            temperatures = stager.stage(seqs, graph_bs, gv)
+            temperatures = stager.stage(seqs, graph_bs, gv, with_temperatures=self.rank == 0)
             ctx.set_context(False, slot_mapping=gv["slot_mapping"][:bs], context_lens=gv["context_lens"][:bs],
                             block_tables=gv["block_tables"][:bs])
             graphs[graph_bs].replay()

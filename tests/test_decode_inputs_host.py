@@ -63,3 +63,22 @@ def test_sections_are_aligned_for_any_batch():
         off = DI.layout(n)
         assert off["tokens"] % 8 == 0 and all(off[k] % 4 == 0 for k in off)
         assert off["lens"] - off["tokens"] == 8 * n and off["blocks"] - off["offsets"] == 4 * (n + 1)
+
+
+def test_worker_ranks_pack_sequences_without_sampling_parameters():
+    """Sequences unpickled on a tensor-parallel worker have no ``temperature`` attribute."""
+    class WorkerSeq:
+        def __init__(self, s):
+            self.last_token, self.num_tokens, self.block_table = s.last_token, s.num_tokens, s.block_table
+
+    seqs = make_seqs(random.Random(3), 9)
+    a = np.zeros(DI.staging_bytes(16, 16), np.uint8)
+    b = np.zeros_like(a)
+    end_a, _ = DI.pack(seqs, a)
+    end_b, _ = DI.pack([WorkerSeq(s) for s in seqs], b, with_temperatures=False)
+    off = DI.layout(9)
+    assert end_a == end_b
+    a[off["temperatures"]:off["offsets"]] = 0
+    assert np.array_equal(a, b)
+    with pytest.raises(AttributeError):
+        DI.pack([WorkerSeq(s) for s in seqs], b)
