@@ -235,7 +235,7 @@ NVLLM_API int nvllm_decode_step_inputs(const void* staged, int64_t tokens_off, i
  * GPU.  Replaces dist.all_reduce in RowParallelLinear.forward (nanovllm/layers/linear.py:195-199)
  * for tensors up to `max_bytes`.  Set-up, once per process and device, outside stream capture:
  *   nvllm_ar_init(rank, world, max_bytes, handle_out)  allocates this rank's flag + staging area
- *       (8 KB + 2 * max_bytes of device memory) and writes its CUDA IPC handle
+ *       (8 KB + 4 * max_bytes of device memory) and writes its CUDA IPC handle
  *       (nvllm_ar_handle_bytes() bytes) to handle_out;
  *   the caller gathers the handles of all ranks (rank order) by its own means;
  *   nvllm_ar_connect(all_handles)  maps every peer's area.

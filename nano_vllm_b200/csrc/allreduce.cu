@@ -6,7 +6,19 @@
 // [batch, hidden] bf16 tensor of 0.5-2 MiB, i.e. latency-bound.  Here every rank owns one device
 // allocation that all its peers map through CUDA IPC:
 //
-//     [ flags: kMaxBlocks x kMaxRanks u32 | epochs: kMaxBlocks u32 | staging 0 | staging 1 ]
+//     [ flags: kMaxBlocks x kMaxRanks u32 | call counts | staging 0 | staging 1 | cells 0 | cells 1 ]
+//
+// Two protocols, chosen by size (the same choice on every rank).
+//
+// SMALL tensors (2 x bytes x world <= max_bytes): flagged cells, in the manner of NCCL's
+// low-latency protocol.  A cell is 16 bytes: 8 bytes of data and the call count twice
+// {d0, count, d1, count}, written with one 16-byte store; each 8-byte half validates itself, so a
+// store that arrives in two halves is harmless.  Every thread pushes its cells straight into the
+// cell area of every peer (region [buffer][source rank]), then polls its OWN area (local memory)
+// until the cells of every peer carry this call's count, and sums in rank order.  No fence, no
+// separate flag round trip, no block-wide barrier: one NVLink crossing of latency.
+//
+// LARGER tensors: staging + flags.
 //
 // One call = one kernel on every rank, same grid everywhere.  Block b of rank r
 //   1. copies its slice of the input into r's staging buffer (e & 1), e = the block's call count,
@@ -36,8 +48,9 @@ constexpr int kThreads = 512;
 constexpr int64_t kFlagBytes = kMaxBlocks * kMaxRanks * 4;
 constexpr int64_t kEpochOff = kFlagBytes;                      // u32[kMaxBlocks]
 constexpr int64_t kBrokenOff = kEpochOff + kMaxBlocks * 4;     // u32 latch
+constexpr int64_t kCellEpochOff = kBrokenOff + 64;             // u32[kMaxBlocks], call counts of the cell protocol
 constexpr int64_t kHeaderBytes = 8192;
-static_assert(kBrokenOff + 4 <= kHeaderBytes, "header");
+static_assert(kCellEpochOff + kMaxBlocks * 4 <= kHeaderBytes, "header");
 
 struct Peers {
   unsigned char* base[kMaxRanks];
@@ -67,6 +80,17 @@ __device__ __forceinline__ uint4 ld_volatile16(const uint4* p) {
   uint4 v;
   asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
+}
+__device__ __forceinline__ void st_volatile16(uint4* p, const uint4& v) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void add4(float (&acc)[4], uint32_t lo, uint32_t hi) {
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&lo));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hi));
+  acc[0] += a.x;
+  acc[1] += a.y;
+  acc[2] += b.x;
+  acc[3] += b.y;
 }
 __device__ __forceinline__ void add8(float (&acc)[8], const uint4& v) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -152,8 +176,95 @@ __device__ void allreduce_block(const Params& p, int rank, int b, int nblocks) {
   if (tid == 0) epochs[b] = e;
 }
 
+// Cell protocol: the work of block `b` on behalf of rank `rank`.  n_cells = ceil(n_elems / 4).
+__device__ void allreduce_cells_block(const Params& p, int rank, int b, int nblocks) {
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_abort;
+  const int tid = threadIdx.x;
+  unsigned char* own = p.peers.base[rank];
+  uint32_t* epochs = reinterpret_cast<uint32_t*>(own + kCellEpochOff);
+  uint32_t* broken = reinterpret_cast<uint32_t*>(own + kBrokenOff);
+  if (tid == 0) {
+    s_epoch = epochs[b] + 1;
+    s_abort = *reinterpret_cast<volatile uint32_t*>(broken) != 0;
+  }
+  __syncthreads();
+  const uint32_t e = s_epoch;
+  const int64_t n_elems = p.n16 * 8 + p.tail_elems;
+  const int64_t n_cells = (n_elems + 3) / 4;
+  const int64_t cells_cap = p.stage_bytes / 16 / p.world;  // cells per source rank in one buffer
+  const int64_t area_off = kHeaderBytes + 2 * p.stage_bytes + static_cast<int64_t>(e & 1) * p.stage_bytes;
+  const int64_t c0 = n_cells * b / nblocks, c1 = n_cells * (b + 1) / nblocks;
+  const uint2* in2 = reinterpret_cast<const uint2*>(p.in);
+  uint2* out2 = reinterpret_cast<uint2*>(p.out);
+  const __nv_bfloat16* in_e = reinterpret_cast<const __nv_bfloat16*>(p.in);
+  __nv_bfloat16* out_e = reinterpret_cast<__nv_bfloat16*>(p.out);
+
+  auto load_own = [&](int64_t c) {
+    if (4 * c + 4 <= n_elems) return in2[c];
+    __nv_bfloat16 t[4];  // the ragged last cell: missing elements are zero
+    for (int k = 0; k < 4; ++k) t[k] = 4 * c + k < n_elems ? in_e[4 * c + k] : __float2bfloat16(0.f);
+    return *reinterpret_cast<const uint2*>(t);
+  };
+
+  // push this rank's cells into every peer's area, region [source = rank]
+  for (int64_t c = c0 + tid; c < c1; c += blockDim.x) {
+    const uint2 d = load_own(c);
+    const uint4 cell = make_uint4(d.x, e, d.y, e);
+    for (int r = 0; r < p.world; ++r) {
+      if (r == rank) continue;
+      uint4* dst = reinterpret_cast<uint4*>(p.peers.base[r] + area_off) + rank * cells_cap + c;
+      st_volatile16(dst, cell);
+    }
+  }
+  // collect: own area, regions [source = r]; sum in rank order
+  bool gave_up = s_abort;
+  for (int64_t c = c0 + tid; c < c1; c += blockDim.x) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < p.world; ++r) {
+      if (r == rank) {
+        const uint2 d = load_own(c);
+        add4(acc, d.x, d.y);
+        continue;
+      }
+      const uint4* src = reinterpret_cast<const uint4*>(own + area_off) + r * cells_cap + c;
+      uint4 v = ld_volatile16(src);
+      if (!gave_up && (v.y != e || v.w != e)) {
+        const long long t0 = clock64();
+        do {
+          v = ld_volatile16(src);
+          if (clock64() - t0 > p.wait_cycles) {
+            atomicOr(p.status, NVLLM_STATUS_TIMEOUT);
+            *reinterpret_cast<volatile uint32_t*>(broken) = 1;
+            gave_up = true;
+            break;
+          }
+        } while (v.y != e || v.w != e);
+      }
+      add4(acc, v.x, v.z);
+    }
+    uint2 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    if (4 * c + 4 <= n_elems) {
+      out2[c] = o;
+    } else {
+      const __nv_bfloat16* t = reinterpret_cast<const __nv_bfloat16*>(&o);
+      for (int k = 0; k < 4; ++k)
+        if (4 * c + k < n_elems) out_e[4 * c + k] = t[k];
+    }
+  }
+  __syncthreads();
+  if (tid == 0) epochs[b] = e;
+}
+
+__device__ __forceinline__ bool use_cells(const Params& p) {
+  return 2 * ((p.n16 * 8 + p.tail_elems + 3) / 4 * 8) * p.world <= p.stage_bytes;
+}
+
 __global__ void __launch_bounds__(kThreads) allreduce_kernel(const Params p) {
-  allreduce_block(p, p.rank, blockIdx.x, gridDim.x);
+  if (use_cells(p)) allreduce_cells_block(p, p.rank, blockIdx.x, gridDim.x);
+  else allreduce_block(p, p.rank, blockIdx.x, gridDim.x);
 }
 
 // All ranks in ONE launch on one device (blockIdx.y = rank; in/out per rank): the only legal way
@@ -171,7 +282,8 @@ __global__ void __launch_bounds__(kThreads) allreduce_emulated_kernel(const EmuP
   if (rank == ep.absent_rank) return;
   p.in = ep.in[rank];
   p.out = ep.out[rank];
-  allreduce_block(p, rank, blockIdx.x, gridDim.x);
+  if (use_cells(p)) allreduce_cells_block(p, rank, blockIdx.x, gridDim.x);
+  else allreduce_block(p, rank, blockIdx.x, gridDim.x);
 }
 
 // ---- host state (one per device of this process) ---------------------------------------------
@@ -217,7 +329,7 @@ extern "C" int nvllm_ar_init(int32_t rank, int32_t world, int64_t max_bytes, voi
     return fail(NVLLM_E_GEOMETRY, "ar_init: rank=%d world=%d invalid (2..%d ranks)", rank, world, ar::kMaxRanks);
   if (max_bytes <= 0 || max_bytes % 16) return fail(NVLLM_E_GEOMETRY, "ar_init: max_bytes must be a positive multiple of 16");
   if (!handle_out) return fail(NVLLM_E_NULL, "ar_init: NULL handle_out");
-  const size_t total = static_cast<size_t>(ar::kHeaderBytes + 2 * max_bytes);
+  const size_t total = static_cast<size_t>(ar::kHeaderBytes + 4 * max_bytes);
   void* p = nullptr;
   cudaError_t e = cudaMalloc(&p, total);
   if (e == cudaSuccess) e = cudaMemset(p, 0, total);
@@ -315,7 +427,7 @@ extern "C" int nvllm_ar_allreduce(const void* in, void* out, int64_t n_elems, vo
 }
 
 extern "C" int64_t nvllm_ar_emulated_scratch_bytes(int32_t world, int64_t max_bytes) {
-  return static_cast<int64_t>(world) * (ar::kHeaderBytes + 2 * max_bytes);
+  return static_cast<int64_t>(world) * (ar::kHeaderBytes + 4 * max_bytes);
 }
 
 extern "C" int nvllm_ar_allreduce_emulated(int32_t world, const void* const* inputs, void* const* outputs, int64_t n_elems,
@@ -340,7 +452,7 @@ extern "C" int nvllm_ar_allreduce_emulated(int32_t world, const void* const* inp
   ep.absent_rank = absent_rank;
   if (!ep.base.status) return fail(NVLLM_E_NO_DEVICE, "ar_allreduce_emulated: no CUDA device is usable");
   for (int r = 0; r < ar::kMaxRanks; ++r) {
-    ep.base.peers.base[r] = r < world ? static_cast<unsigned char*>(scratch) + r * (ar::kHeaderBytes + 2 * max_bytes) : nullptr;
+    ep.base.peers.base[r] = r < world ? static_cast<unsigned char*>(scratch) + r * (ar::kHeaderBytes + 4 * max_bytes) : nullptr;
     ep.in[r] = r < world ? static_cast<const uint4*>(inputs[r]) : nullptr;
     ep.out[r] = r < world ? static_cast<uint4*>(outputs[r]) : nullptr;
     if (r < world && (!aligned16(inputs[r]) || !aligned16(outputs[r])))

@@ -38,12 +38,14 @@ def test_emulated_ranks_sum_bit_exactly_call_after_call(cuda, world):
     assert _lib.read_status() == 0
 
 
-def test_absent_peer_times_out_without_hanging(cuda):
+@pytest.mark.parametrize("n", [4096, 1024 * 1024 + 8])
+def test_absent_peer_times_out_without_hanging(cuda, n):
     """Rank 1 never arrives: the others give up after the clock limit, set the TIMEOUT bit and a
-    latch, and later calls return at once instead of waiting again."""
+    latch, and later calls return at once instead of waiting again.  Both protocols: flagged
+    cells (small tensor) and staging + flags (large tensor)."""
     import time
     scratch = _scratch(cuda, 2)
-    xs = [torch.ones(4096, dtype=torch.bfloat16, device=cuda) for _ in range(2)]
+    xs = [torch.ones(n, dtype=torch.bfloat16, device=cuda) for _ in range(2)]
     t0 = time.time()
     AR.all_reduce_emulated(xs, scratch, MAX_BYTES, absent_rank=1)
     torch.cuda.synchronize()
