@@ -23,7 +23,7 @@ os.chdir(tempfile.mkdtemp())
 e2e.GEOMETRY["tiny"] = dict(hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
                             head_dim=128, intermediate_size=512, tie_word_embeddings=True)
 llm = e2e.make_engine(e2e.write_model_dir("tiny"), %(attn)r, %(ref)r, enforce_eager=False, max_model_len=2048,
-                      max_num_seqs=16, tensor_parallel_size=1)
+                      max_num_seqs=16, tensor_parallel_size=%(tp)d)
 from nanovllm.sampling_params import SamplingParams
 random.seed(1)
 prompts = [[random.randint(0, 151935) for _ in range(n)] for n in (300, 700, 257, 1100, 90)]
@@ -39,8 +39,8 @@ print(json.dumps({"lens": [len(x["token_ids"]) for x in first + second], "same":
 """
 
 
-def _run(attn):
-    code = SCRIPT % {"root": str(ROOT), "ref": str(REF), "attn": attn}
+def _run(attn, tp=1):
+    code = SCRIPT % {"root": str(ROOT), "ref": str(REF), "attn": attn, "tp": tp}
     proc = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, cwd=str(ROOT))
     assert proc.returncode == 0, proc.stderr[-3000:]
     return json.loads([ln for ln in proc.stdout.splitlines() if ln.startswith("{")][-1])
@@ -63,3 +63,19 @@ def test_one_launch_decode_inputs_and_fused_sampler_change_no_greedy_token():
     stock_path, fused_path = _run("b200-fused"), _run("b200-full")
     assert fused_path["status"] == 0 and fused_path["lens"] == [40] * 10
     assert fused_path["tokens"] == stock_path["tokens"]
+
+
+def _gpus():
+    import torch
+    return torch.cuda.device_count()
+
+
+@pytest.mark.skipif(_gpus() < 2, reason="needs two GPUs")
+def test_tensor_parallel_engine_with_every_optional_step():
+    """Two ranks (rank 0 plus a spawned worker that receives pickled sequences without sampling
+    parameters): head-sharded attention, fused pre-attention, one-launch decode inputs on both
+    ranks, the sampler on rank 0, and the peer-memory all-reduce behind both row-parallel
+    projections, with decode graphs captured around them."""
+    d = _run("b200-full-ar", tp=2)
+    assert d["lens"] == [40] * 10 and d["status"] == 0 and d["launches"] > 0
+    assert d["same"] >= 0.9 * d["total"], d
