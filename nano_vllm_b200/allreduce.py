@@ -44,6 +44,18 @@ class PeerAllReduce:
         return (x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.data_ptr() % 16 == 0
                 and (x.numel() * 2 + 15) // 16 * 16 <= self.max_bytes)
 
+    def preferred(self, x: torch.Tensor) -> bool:
+        """Whether this kernel is expected to beat the library collective for ``x``: always at two
+        ranks (measured up to 4 MiB); at more ranks only while the flagged-cell protocol applies
+        and a rank pushes at most 8 MiB in total (2 x bytes to each peer) -- an estimate from the
+        two-rank measurements, larger worlds were not measured."""
+        if not self.fits(x):
+            return False
+        nbytes = x.numel() * 2
+        if self.world == 2:
+            return True
+        return 2 * nbytes * self.world <= self.max_bytes and 2 * nbytes * (self.world - 1) <= (8 << 20)
+
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if not self.fits(x):
             raise RuntimeError("PeerAllReduce.all_reduce: contiguous 16-byte-aligned bf16 CUDA tensor of at most "

@@ -103,8 +103,8 @@ def fuse_decode_inputs() -> None:
 def fuse_all_reduce(max_bytes: int = 8 << 20, wait_ms: int = 60000) -> None:
     """Optional step for tensor-parallel runs: ``RowParallelLinear.forward``
     (nanovllm/layers/linear.py:195-199) sums its partial outputs with the peer-memory kernel
-    (allreduce.PeerAllReduce) when the tensor fits its staging buffers, and with
-    ``dist.all_reduce`` otherwise (prefill-sized tensors).  The peer mapping is made at the first
+    (allreduce.PeerAllReduce) where that is expected to be the faster one (decode-sized tensors;
+    see PeerAllReduce.preferred), and with ``dist.all_reduce`` otherwise (prefill-sized tensors).  The peer mapping is made at the first
     call outside stream capture, which every rank reaches at the same point (the engine's warm-up
     forward).  Ranks of the engine run loosely coupled (a worker can be seconds behind while it
     compiles or captures), hence the long default wait."""
@@ -121,7 +121,7 @@ def fuse_all_reduce(max_bytes: int = 8 << 20, wait_ms: int = 60000) -> None:
             ar = state["ar"]
             if ar is None and not torch.cuda.is_current_stream_capturing():
                 ar = state["ar"] = PeerAllReduce(dist.get_rank(), dist.get_world_size(), max_bytes, wait_ms=wait_ms)
-            if ar is not None and ar.fits(y):
+            if ar is not None and ar.preferred(y):
                 ar.all_reduce(y)
             else:
                 dist.all_reduce(y)
