@@ -394,11 +394,13 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
       const int srow = lane >> 2, spiece = lane & 3;
       __nv_bfloat16* out_tile = p.out + static_cast<int64_t>(x.q0 + x.m0) * p.out_stride + x.h * D;
       const int toks_valid = min(BMT, x.Lq - x.m0);
+      uint32_t ob[2][32];  // the load of the next 32 columns runs under the stores of the current ones
+      tmem_ld32(tmem_o + lane_addr, ob[0]);
 #pragma unroll
       for (int c = 0; c < OCH; ++c) {
-        uint32_t o[32];
-        tmem_ld32(tmem_o + lane_addr + c * 32, o);
+        uint32_t(&o)[32] = ob[c & 1];
         tmem_wait_ld();
+        if (c + 1 < OCH) tmem_ld32(tmem_o + lane_addr + (c + 1) * 32, ob[(c + 1) & 1]);
         if (c == OCH - 1) {  // O is in registers: the next item's first product may overwrite it
           tc_fence_before();
           __syncwarp();
