@@ -62,7 +62,7 @@ extern "C" int nvllm_prefill_varlen(const void* q, int64_t q_row_stride, const v
   p.hkv = num_kv_heads;
   p.g = num_q_heads / num_kv_heads;
   p.d = head_dim;
-  p.pack_log2 = 0;
+  p.pack = 1;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.num_blocks = num_blocks;
   // NVLLM_PREFILL_IMPL = mma | tc | tcp picks a kernel by hand (measurement and test aid, read on

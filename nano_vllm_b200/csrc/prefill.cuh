@@ -20,7 +20,7 @@ struct PrefillParams {
   const int32_t* cu_k;
   int batch, max_seqlen_q, max_seqlen_k;
   int hq, hkv, g, d;
-  int pack_log2;  // persistent tcgen05 kernel only: log2 of the query heads packed into one tile
+  int pack;  // persistent tcgen05 kernel only: query heads packed into one tile (1..8)
   float scale_log2e;
   int64_t num_blocks;
   int* status;

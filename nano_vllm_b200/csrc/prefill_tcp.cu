@@ -76,7 +76,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
                    const int counter_slot) {
   using namespace tcp;
   using G = Geo<D>;
-  constexpr int Q_BYTES = G::Q_BYTES, Q_SUB = G::Q_SUB, KV_BYTES = G::KV_BYTES, KV_SUB = G::KV_SUB;
+  constexpr int Q_SUB = G::Q_SUB, KV_BYTES = G::KV_BYTES, KV_SUB = G::KV_SUB;
   constexpr int OFF_Q = G::OFF_Q, OFF_K = G::OFF_K, OFF_V = G::OFF_V, OFF_CTRL = G::OFF_CTRL;
   constexpr int OFF_SLOTS = G::OFF_SLOTS, OFF_MISC = G::OFF_MISC, OFF_PREFIX = G::OFF_PREFIX;
   constexpr int OCH = G::OCH, PIECES = G::PIECES;
@@ -91,11 +91,11 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + OFF_MISC + 8);
   int* prefix = reinterpret_cast<int*>(base_ptr + OFF_PREFIX);  // prefix[b] = query tiles before sequence b
-  // Head packing: the 128 rows of a tile are BMT = 128 >> pl query tokens x (1 << pl) query heads
-  // of one KV head (row = token * heads + head), so short and ragged sequences waste fewer rows
-  // above the diagonal and past their end, and the packed heads share every K/V tile.
-  static_assert(BM == 128, "the tile-count shift below assumes 128 rows");
-  const int pl = p.pack_log2, BMT = BM >> pl;
+  // Head packing: the rows of a tile are BMT = 128 / n query tokens x n query heads of one KV head
+  // (row = token * n + head; n = p.pack need not be a power of two: 7 heads x 18 tokens leave two
+  // rows unused), so short and ragged sequences waste fewer rows above the diagonal and past
+  // their end, and the packed heads share every K/V tile.
+  const int pack = p.pack, BMT = BM / pack;
 
   if (warp == 4) {
     // query tiles per sequence -> exclusive prefix sum (warp scan, 32 sequences at a time)
@@ -103,7 +103,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
     for (int b0 = 0; b0 < p.batch; b0 += 32) {
       const int b = b0 + lane;
       int tiles = 0;
-      if (b < p.batch) tiles = (p.cu_q[b + 1] - p.cu_q[b] + BMT - 1) >> (7 - pl);
+      if (b < p.batch) tiles = (p.cu_q[b + 1] - p.cu_q[b] + BMT - 1) / BMT;
       int incl = tiles;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
@@ -146,7 +146,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
   if (warp == 4) {
     // ------------------------------------------------------------------ producer lane
     if (lane == 0) {
-      const int hgroups = p.hq >> pl;
+      const int hgroups = p.hq / pack;
       const int total_items = prefix[p.batch] * hgroups;
       int T = 0;   // key tiles loaded so far in this block's life
       int nq = 0;  // items with at least one key tile so far (Q_FULL phase)
@@ -159,7 +159,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
           const unsigned idx = atomicAdd(&g_item_counter[counter_slot], 1u);
           if (idx >= static_cast<unsigned>(total_items)) break;
           const int pi = idx / hgroups;
-          x.h = (idx - pi * hgroups) << pl;  // first of the packed heads
+          x.h = (idx - pi * hgroups) * pack;  // first of the packed heads
           int lo = 0, hi = p.batch;  // largest b with prefix[b] <= pi
           while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
@@ -179,7 +179,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
           // never produces): the rows are zero; written here, the other roles never see it.
           for (int r = x.m0; r < min(x.m0 + BMT, x.Lq); ++r) {
             uint4* dst = reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(x.q0 + r) * p.out_stride + x.h * D);
-            for (int c = 0; c < (PIECES << pl); ++c) dst[c] = make_uint4(0, 0, 0, 0);  // the packed heads are adjacent
+            for (int c = 0; c < PIECES * pack; ++c) dst[c] = make_uint4(0, 0, 0, 0);  // the packed heads are adjacent
           }
         }
         if (it >= 2 && !wait_or_abort(bar(ITEM_FREE0 + (it & 1)), ((it >> 1) - 1) & 1, abort_flag)) break;
@@ -192,7 +192,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
         const int kvh = x.h / p.g;
         // Q buffer: free once the last S product of the previous item is complete
         if (T > 0 && !wait_or_abort(bar(QK_DONE0 + ((T - 1) & 1)), ((T - 1) >> 1) & 1, abort_flag)) break;
-        mbar_expect_tx(bar(Q_FULL), Q_BYTES);
+        mbar_expect_tx(bar(Q_FULL), G::NSUB * pack * BMT * 128);  // the box holds pack x BMT rows per sub-tile
         tma_load_3d(base + OFF_Q, &tmap_q, bar(Q_FULL), 0, x.h, x.q0 + x.m0);
         if constexpr (G::NSUB == 2) tma_load_3d(base + OFF_Q + Q_SUB, &tmap_q, bar(Q_FULL), 64, x.h, x.q0 + x.m0);
         ++nq;
@@ -286,6 +286,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
   } else {
     // ------------------------------------------------------------------ softmax rows
     const int r = warp * 32 + lane;
+    const int r_tok = r / pack;  // this row's token within the tile (== BMT for the unused rows of a 7-head tile)
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     unsigned char* stage = base_ptr + G::OFF_STAGE + warp * 2048;  // this warp's 32 rows x 64 B
     int T = 0;
@@ -294,7 +295,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
       if (!(ok = wait_or_abort(bar(ITEM_FULL0 + (it & 1)), (it >> 1) & 1, abort_flag))) break;
       const Item x = read_item(it);
       if (x.n_kv < 0) break;
-      const int qi = x.m0 + (r >> pl), off = x.Lk - x.Lq;
+      const int qi = x.m0 + r_tok, off = x.Lk - x.Lq;
       float m_used = -INFINITY, l = 0.f;
       for (int j = 0; j < x.n_kv; ++j) {
         const int t = T + j, st = t & 1, ph = (t >> 1) & 1;
@@ -420,7 +421,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
         for (int i = 0; i < 4; ++i) {
           const int lr = i * 8 + srow;       // row within the warp's 32
           const int row = warp * 32 + lr;    // row of the tile
-          const int tok = row >> pl, hh = row & ((1 << pl) - 1);
+          const int tok = row / pack, hh = row - tok * pack;
           const uint4 v = *reinterpret_cast<const uint4*>(stage + lr * 64 + ((spiece ^ ((lr >> 1) & 3)) << 4));
           if (tok < toks_valid)
             *reinterpret_cast<uint4*>(out_tile + static_cast<int64_t>(tok) * p.out_stride + hh * D + c * 32 + spiece * 8) = v;
@@ -465,14 +466,15 @@ static int launch_prefill_tcp_t(const PrefillParams& p_in, int64_t total_q, int6
     if (e != cudaSuccess) return fail(NVLLM_E_CUDA, "prefill (persistent): set-up failed: %s", cudaGetErrorString(e));
     attr_done[dev] = true;
   }
-  // heads packed into a query tile: the largest power of two that divides the group size, at most 8
-  // (NVLLM_PREFILL_PACK = 1 | 2 | 4 | 8 caps it; measurement aid, read on every call)
+  // heads packed into a query tile: the largest divisor of the group size that is at most 8
+  // (NVLLM_PREFILL_PACK = 1..8 caps it; measurement aid, read on every call)
   int cap = 8;
   if (const char* s = std::getenv("NVLLM_PREFILL_PACK")) cap = std::atoi(s);
   PrefillParams p = p_in;
-  p.pack_log2 = 0;
-  while (p.pack_log2 < 3 && (2 << p.pack_log2) <= cap && p.g % (2 << p.pack_log2) == 0) ++p.pack_log2;
-  const int pack = 1 << p.pack_log2, bmt = tc::BM >> p.pack_log2;
+  p.pack = 1;
+  for (int n = 2; n <= 8 && n <= cap; ++n)
+    if (p.g % n == 0) p.pack = n;
+  const int pack = p.pack, bmt = tc::BM / pack;
   CUtensorMap mq, mk, mv;
   if (!make_tmap_3d(&mq, p.q, D, p.hq, total_q, D, p.q_stride, bmt, pack)) return NVLLM_E_CUDA;
   if (p.block_tables) {

@@ -39,7 +39,7 @@ def test_cfg2(cuda):
 
 
 @pytest.mark.parametrize("hq,hkv,d", [(16, 8, 128), (32, 8, 128), (14, 2, 64), (4, 1, 128), (2, 2, 64),
-                                      (8, 1, 128), (12, 2, 64), (16, 2, 64)])
+                                      (8, 1, 128), (12, 2, 64), (16, 2, 64), (10, 2, 128), (6, 2, 128), (14, 2, 128)])
 def test_packed_lengths(cuda, hq, hkv, d):
     case = W.make_prefill_case(21, 8, 1, 1, hq, hkv, d, share_every=0,
                                lengths=[1, 100, 127, 128, 129, 256, 257, 1024])
@@ -105,12 +105,14 @@ def test_many_sequences_through_the_persistent_kernel(cuda):
     _check(cuda, case, "150 sequences")
 
 
-@pytest.mark.parametrize("cap", [1, 2, 4, 8])
+@pytest.mark.parametrize("cap", [1, 2, 3, 4, 8])
 @pytest.mark.parametrize("d", [64, 128])
 def test_head_packing_of_the_persistent_kernel(cuda, monkeypatch, cap, d):
     """The persistent kernel packs up to 8 query heads of one KV head into the 128 rows of a tile
-    (16 to 128 tokens per tile); NVLLM_PREFILL_PACK caps the number.  Every packing must agree
-    with the oracle on ragged packed input and on prefix-cached input."""
+    (16 to 128 tokens per tile; the number of heads is the largest divisor of the group size
+    within the cap, so 3, 5, 6 or 7 heads leave a few rows unused); NVLLM_PREFILL_PACK caps the
+    number.  Every packing must agree with the oracle on ragged packed input and on
+    prefix-cached input."""
     monkeypatch.setenv("NVLLM_PREFILL_IMPL", "tcp")
     monkeypatch.setenv("NVLLM_PREFILL_PACK", str(cap))
     case = W.make_prefill_case(28, 9, 1, 1, 16, 2, d, share_every=0,
