@@ -6,6 +6,12 @@ nanovllm/layers/attention.py:32-79) and makes the layer read nano-vllm's own per
 (nanovllm/utils/context.py:16-17).  Call it before ``nanovllm.models`` is imported (i.e. before
 ``from nanovllm import LLM``), because the model files bind ``Attention`` at import time
 (nanovllm/models/qwen3.py:8).
+
+Optional steps after ``install()``, each replacing one method of the engine by a version that
+calls this package: ``fuse_pre_attention()`` (q/k norm + rotary + KV store in one launch),
+``fuse_sampler()`` (one-pass token sampling), ``fuse_decode_inputs()`` (decode-step inputs in
+one copy and one launch) and, for tensor-parallel runs, ``fuse_all_reduce()`` (peer-memory sum
+behind the row-parallel projections).
 """
 from __future__ import annotations
 
