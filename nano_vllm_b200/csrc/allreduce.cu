@@ -30,8 +30,9 @@
 // Every rank adds the same numbers in the same order, so all ranks hold bit-identical results.
 // Two staging buffers used in turn need no closing barrier: a peer cannot reach call e+2 (which
 // overwrites buffer e & 1) before this rank has published e+1, which it does after reading.
-// All loads of peer memory are plain 16-byte loads issued by each block itself (no multicast
-// object, no TMA); flags and epochs live in device memory, so a captured graph replays correctly.
+// All accesses to peer memory are plain 16-byte loads and stores issued by each thread itself:
+// no bulk-copy engine and no switch-side broadcast or reduction object is involved.  Flags and
+// call counts live in device memory, so a captured graph replays correctly.
 #include <cooperative_groups.h>
 
 #include <cstring>
