@@ -91,3 +91,30 @@ def sampler_cases():
             torch.random.set_rng_state(state)
         out[name] = (logits, t, noise, tokens)
     return out
+
+
+# ---- decode-step inputs ------------------------------------------------------------------------
+
+class DecodeSeq:
+    """The attributes of a nano-vllm Sequence that a decode step reads."""
+
+    def __init__(self, last_token, num_tokens, temperature, block_table):
+        self.last_token, self.num_tokens, self.temperature, self.block_table = last_token, num_tokens, temperature, block_table
+
+
+def decode_input_cases():
+    """name -> (sequences, recorded) where ``recorded`` holds what nano-vllm's own
+    prepare_decode / prepare_block_tables / prepare_sample returned for them
+    (make_decode_inputs_golden.py)."""
+    import numpy as np
+    z = np.load(GOLDEN_DIR / "decode_inputs.npz")
+    out = {}
+    for name in sorted({k.split(".")[0] for k in z.files}):
+        lens = z[f"{name}.table_len"]
+        ends = np.cumsum(lens)
+        flat = z[f"{name}.table_flat"]
+        seqs = [DecodeSeq(int(z[f"{name}.last_token"][i]), int(z[f"{name}.num_tokens"][i]), float(z[f"{name}.temperatures"][i]),
+                          [int(b) for b in flat[ends[i] - lens[i]:ends[i]]]) for i in range(len(lens))]
+        rec = {k: z[f"{name}.{k}"] for k in ("input_ids", "positions", "slot_mapping", "context_lens", "block_tables", "temperatures")}
+        out[name] = (seqs, rec)
+    return out

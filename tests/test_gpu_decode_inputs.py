@@ -6,6 +6,12 @@ import numpy as np
 import pytest
 import torch
 
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent / "golden"))
+import cases as C  # noqa: E402
+
 from nano_vllm_b200 import _lib, decode_inputs as DI
 from oracle import paged_attention_ref as R
 from test_decode_inputs_host import make_seqs
@@ -67,3 +73,20 @@ def test_bad_arguments_are_refused(cuda, lib):
     assert call(batch=9) == -3 and call(used_width=17) == -3 and call(stride=8) == -3 and call(table_width=0) == -3
     assert call(tokens_off=4) == -2 and call(lens_off=2) == -2
     assert b"decode_step_inputs" in lib.nvllm_last_error()
+
+
+@pytest.mark.parametrize("name", ["few", "graph_batch", "one", "ragged"])
+def test_recorded_reference_batches(cuda, name):
+    """Batches for which nano-vllm's own prepare_decode / prepare_sample output was recorded."""
+    seqs, rec = C.decode_input_cases()[name]
+    n, widest = len(seqs), rec["block_tables"].shape[1]
+    gbs = next(x for x in GRAPH_BS if x >= n)
+    gv = _graph_vars(cuda, 512, 16, 9)
+    temps = DI.DecodeInputStager(512, 16, cuda).stage(seqs, gbs, gv)
+    torch.cuda.synchronize()
+    for k in ("input_ids", "positions", "slot_mapping", "context_lens"):
+        got = gv[k][:gbs].cpu().numpy()
+        assert np.array_equal(got[:n], rec[k]) and not got[n:].any(), k
+    bt = gv["block_tables"][:gbs].cpu().numpy()
+    assert np.array_equal(bt[:n, :widest], rec["block_tables"]) and not bt[:, widest:].any() and not bt[n:].any()
+    assert np.array_equal(temps.cpu().numpy(), rec["temperatures"])

@@ -68,3 +68,16 @@ def test_sampler_oracle_matches_reference(name):
     assert torch.equal(R.sampler_ref(logits, temperatures, noise), tokens)
     greedy = temperatures == 0
     assert greedy.any() and torch.equal(tokens[greedy], logits.float().argmax(-1)[greedy])
+
+
+@pytest.mark.parametrize("name", ["few", "graph_batch", "one", "ragged"])
+def test_decode_inputs_oracle_matches_reference(name):
+    """The restated buffer contents against what nano-vllm's own prepare_decode returned."""
+    seqs, rec = C.decode_input_cases()[name]
+    n, widest = len(seqs), rec["block_tables"].shape[1]
+    ref = R.decode_inputs_ref(seqs, n + 3, widest + 2)   # a graph batch and a table wider than the step
+    for k in ("input_ids", "positions", "slot_mapping", "context_lens"):
+        assert ref[k].dtype == rec[k].dtype and np.array_equal(ref[k][:n], rec[k]), k
+        assert not ref[k][n:].any()
+    assert np.array_equal(ref["block_tables"][:n, :widest], rec["block_tables"])
+    assert not ref["block_tables"][:, widest:].any() and not ref["block_tables"][n:].any()
