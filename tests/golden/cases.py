@@ -118,3 +118,23 @@ def decode_input_cases():
         rec = {k: z[f"{name}.{k}"] for k in ("input_ids", "positions", "slot_mapping", "context_lens", "block_tables", "temperatures")}
         out[name] = (seqs, rec)
     return out
+
+
+# ---- pre-attention step ------------------------------------------------------------------------
+
+def pre_attention_cases():
+    """name -> dict of what make_pre_attention_golden.py recorded from nano-vllm's own RMSNorm and
+    RotaryEmbedding modules: inputs (qkv, positions, norm weights or None), geometry, outputs."""
+    import numpy as np
+    z = np.load(GOLDEN_DIR / "pre_attention.npz")
+    bf16 = lambda a: torch.from_numpy(a.copy()).view(torch.bfloat16)
+    out = {}
+    for name in sorted({k.split(".")[0] for k in z.files}):
+        hq, hkv, d, norm, max_pos = (int(v) for v in z[f"{name}.geometry"])
+        out[name] = dict(hq=hq, hkv=hkv, d=d, max_pos=max_pos, base=float(z[f"{name}.rope_base"]),
+                         qkv=bf16(z[f"{name}.qkv"]), positions=torch.from_numpy(z[f"{name}.positions"].copy()),
+                         q_weight=bf16(z[f"{name}.q_weight"]) if norm else None,
+                         k_weight=bf16(z[f"{name}.k_weight"]) if norm else None,
+                         q=bf16(z[f"{name}.q"]), k=bf16(z[f"{name}.k"]),
+                         cache_rows=torch.from_numpy(z[f"{name}.cache_rows"].copy()))
+    return out

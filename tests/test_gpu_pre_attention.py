@@ -1,7 +1,13 @@
 """Fused q/k RMSNorm + rotary embedding + KV-cache store on the GPU against the CPU
 restatement of the reference's separate ops."""
+import sys
+from pathlib import Path
+
 import pytest
 import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parent / "golden"))
+import cases as C  # noqa: E402
 
 from nano_vllm_b200 import _lib, attention as A
 from oracle import paged_attention_ref as R
@@ -77,3 +83,21 @@ def test_fused_pre_attention_without_a_cache_is_rotation_only(cuda):
     q_d, k_d, _ = qkv_d.cpu().split([hq * d, hkv * d, hkv * d], dim=-1)
     _bf16_ulp_close(q_d.reshape(n, hq, d), q_ref, "q")
     _bf16_ulp_close(k_d.reshape(n, hkv, d), k_ref, "k")
+
+
+@pytest.mark.parametrize("name", ["qwen2", "qwen3", "qwen3_8b_shard"])
+def test_recorded_reference_modules(cuda, name):
+    """Inputs for which the output of nano-vllm's own RMSNorm and RotaryEmbedding modules was
+    recorded (tests/golden/make_pre_attention_golden.py)."""
+    c = C.pre_attention_cases()[name]
+    hq, hkv, d, n = c["hq"], c["hkv"], c["d"], c["qkv"].shape[0]
+    cache = R.rotary_cache_ref(d, c["max_pos"], c["base"]).to(cuda)
+    qkv = c["qkv"].to(cuda)
+    empty = torch.zeros(0, dtype=torch.bfloat16, device=cuda)
+    A.qk_norm_rope_store(qkv, c["positions"].to(cuda), c["q_weight"].to(cuda) if c["q_weight"] is not None else None,
+                         c["k_weight"].to(cuda) if c["k_weight"] is not None else None, cache, 1e-6,
+                         torch.zeros(0, dtype=torch.int32, device=cuda), empty, empty, hq, hkv, d)
+    q_d, k_d, v_d = qkv.cpu().split([hq * d, hkv * d, hkv * d], dim=-1)
+    _bf16_ulp_close(q_d.reshape(n, hq, d), c["q"], "q")
+    _bf16_ulp_close(k_d.reshape(n, hkv, d), c["k"], "k")
+    assert torch.equal(v_d, c["qkv"][:, (hq + hkv) * d:])

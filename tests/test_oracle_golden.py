@@ -81,3 +81,16 @@ def test_decode_inputs_oracle_matches_reference(name):
         assert not ref[k][n:].any()
     assert np.array_equal(ref["block_tables"][:n, :widest], rec["block_tables"])
     assert not ref["block_tables"][:, widest:].any() and not ref["block_tables"][n:].any()
+
+
+@pytest.mark.parametrize("name", ["qwen2", "qwen3", "qwen3_8b_shard"])
+def test_pre_attention_oracle_matches_reference(name):
+    """q/k RMSNorm + rotary embedding: the restatement against nano-vllm's own modules, bit for bit."""
+    c = C.pre_attention_cases()[name]
+    cache = R.rotary_cache_ref(c["d"], c["max_pos"], c["base"])
+    rows = torch.tensor([0, 1, c["max_pos"] // 2, c["max_pos"] - 1])
+    assert torch.equal(cache[rows], c["cache_rows"])
+    q, k, v = R.qk_norm_rope_ref(c["qkv"], c["positions"], c["q_weight"], c["k_weight"], cache, 1e-6, c["hq"], c["hkv"], c["d"])
+    assert torch.equal(q.view(torch.int16), c["q"].view(torch.int16))
+    assert torch.equal(k.view(torch.int16), c["k"].view(torch.int16))
+    assert torch.equal(v.reshape(v.shape[0], -1), c["qkv"][:, (c["hq"] + c["hkv"]) * c["d"]:])
