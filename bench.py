@@ -162,10 +162,21 @@ def cpu_sample(case, n_seqs):
                         torch.zeros(n_seqs, dtype=torch.int32), case.scale)
 
 
+def use_all_host_threads():
+    """The launcher for several ranks exports OMP_NUM_THREADS=1, which would leave the CPU path on
+    one thread; give it what a single-process run gets by default (one thread per CPU this
+    process may run on)."""
+    import torch
+    if os.environ.get("OMP_NUM_THREADS") == "1" and hasattr(os, "sched_getaffinity"):
+        torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    return torch.get_num_threads()
+
+
 def time_cpu_reference(host_case, steps, warmup):
     import torch
     from nano_vllm_b200 import workloads as W
     from oracle import paged_attention_ref as R
+    use_all_host_threads()
     B, Hq, Hkv, D = host_case.geometry
     nbytes = W.decode_bytes(host_case.context_lens, Hq, Hkv, D)
     fn = lambda: R.decode_ref(host_case.q, host_case.k_cache, host_case.v_cache, host_case.context_lens,
