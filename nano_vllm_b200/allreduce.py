@@ -25,6 +25,19 @@ def gather_handles(handle: bytes, rank: int, world: int, dist=None) -> bytes:
     return b"".join(parts)
 
 
+def prefer_peer_kernel(nbytes: int, world: int, max_bytes: int) -> bool:
+    """Whether the peer-memory kernel is expected to beat the library collective for a tensor of
+    ``nbytes``: always at two ranks (measured up to 4 MiB); at more ranks only while the
+    flagged-cell protocol applies (2 x nbytes x world <= max_bytes) and a rank pushes at most
+    8 MiB in total (2 x nbytes to each peer) -- an estimate from the two-rank measurements, larger
+    worlds were not measured."""
+    if nbytes <= 0 or (nbytes + 15) // 16 * 16 > max_bytes:
+        return False
+    if world == 2:
+        return True
+    return 2 * nbytes * world <= max_bytes and 2 * nbytes * (world - 1) <= (8 << 20)
+
+
 class PeerAllReduce:
     """``all_reduce(x)`` sums a contiguous bf16 CUDA tensor over the ranks in place.  Every rank
     must construct it at the same point and make the same calls."""
@@ -45,16 +58,8 @@ class PeerAllReduce:
                 and (x.numel() * 2 + 15) // 16 * 16 <= self.max_bytes)
 
     def preferred(self, x: torch.Tensor) -> bool:
-        """Whether this kernel is expected to beat the library collective for ``x``: always at two
-        ranks (measured up to 4 MiB); at more ranks only while the flagged-cell protocol applies
-        and a rank pushes at most 8 MiB in total (2 x bytes to each peer) -- an estimate from the
-        two-rank measurements, larger worlds were not measured."""
-        if not self.fits(x):
-            return False
-        nbytes = x.numel() * 2
-        if self.world == 2:
-            return True
-        return 2 * nbytes * self.world <= self.max_bytes and 2 * nbytes * (self.world - 1) <= (8 << 20)
+        """``fits(x)`` and ``prefer_peer_kernel`` for its size."""
+        return self.fits(x) and prefer_peer_kernel(x.numel() * 2, self.world, self.max_bytes)
 
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if not self.fits(x):

@@ -95,3 +95,14 @@ def test_algorithmic_work_formulas():
     assert W.store_bytes(10, 1024) == 10 * 1024 * 8 + 40
     assert W.prefill_flops([3], [3], 1, 1) == 4 * 6
     assert W.prefill_flops([2], [258], 2, 64) == 4 * 2 * 64 * (2 * 256 + 3)
+
+
+def test_when_the_peer_memory_all_reduce_is_preferred():
+    """Decode-sized tensors go to the peer kernel, prefill-sized ones to the library collective."""
+    from nano_vllm_b200.allreduce import prefer_peer_kernel as prefer
+    mb = 8 << 20
+    assert prefer(256 * 1024 * 2, 2, mb) and prefer(256 * 4096 * 2, 2, mb) and prefer(4 << 20, 2, mb)
+    assert not prefer(16384 * 1024 * 2, 2, mb)            # a 16k-token prefill batch: 32 MiB
+    assert prefer(256 * 1024 * 2, 4, mb) and prefer(256 * 1024 * 2, 8, mb)
+    assert not prefer(256 * 4096 * 2, 4, mb) and not prefer(256 * 4096 * 2, 8, mb)
+    assert not prefer(0, 2, mb)
