@@ -63,3 +63,30 @@ assert q3.Qwen3Attention.forward is not before and q2.Qwen2Attention.forward.__n
 print("ok")
 """)
     assert out == "ok"
+
+
+def test_optional_steps_replace_exactly_one_method_each():
+    out = _run(PRELUDE + """
+from nano_vllm_b200 import plugin
+plugin.install()
+import nanovllm.layers.sampler as sampler, nanovllm.layers.linear as linear, nanovllm.engine.model_runner as mr
+before = (sampler.Sampler.forward, mr.ModelRunner.run, linear.RowParallelLinear.forward)
+keep = (mr.ModelRunner.prepare_prefill, mr.ModelRunner.run_model, linear.ColumnParallelLinear.forward)
+plugin.fuse_sampler(seed=1)
+plugin.fuse_decode_inputs()
+plugin.fuse_all_reduce()
+after = (sampler.Sampler.forward, mr.ModelRunner.run, linear.RowParallelLinear.forward)
+assert all(a is not b for a, b in zip(after, before))
+assert keep == (mr.ModelRunner.prepare_prefill, mr.ModelRunner.run_model, linear.ColumnParallelLinear.forward)
+# without a GPU nothing of the package can run: the replaced method must fail loudly, not fall back
+import torch
+if not torch.cuda.is_available():
+    try:
+        sampler.Sampler().forward(torch.zeros(2, 8), torch.zeros(2))
+        print("fell back")
+    except (AssertionError, RuntimeError, ImportError):
+        print("ok")
+else:
+    print("ok")
+""")
+    assert out == "ok"
