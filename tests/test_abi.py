@@ -76,3 +76,18 @@ def test_null_and_misaligned_arguments_are_rejected_before_any_launch(lib):
     assert rc == -3
     assert lib.nvllm_prefill_varlen(p16, 2048, p16, 1024, p16, 1024, None, 0, 0, p16, 2048, p16, p16, 0, 0, 0, 0, 0,
                                     16, 8, 128, ctypes.c_float(0.1), 0, None) == 0  # empty batch
+
+
+def test_public_header_is_valid_c99_and_cxx():
+    """The header is the contract for bindings in any language: it must compile on its own as
+    plain C (no C++-isms, no CUDA or torch types) and as C++."""
+    import shutil
+    import subprocess
+    from pathlib import Path
+    header = Path(__file__).resolve().parents[1] / "include" / "nvllm_b200.h"
+    if not shutil.which("gcc"):
+        pytest.skip("no gcc")
+    for cmd in (["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", "-x", "c", str(header)],
+                ["g++", "-std=c++17", "-Wall", "-Werror", "-fsyntax-only", "-x", "c++", str(header)]):
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        assert proc.returncode == 0, proc.stderr
