@@ -12,7 +12,7 @@ from oracle import paged_attention_ref as R
 pytestmark = pytest.mark.gpu
 
 GEOMS = [(16, 8, 128), (32, 8, 128), (14, 2, 64), (4, 4, 128), (8, 1, 64)]
-COMMON = dict(deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture, HealthCheck.too_slow])
+COMMON = dict(deadline=None, derandomize=True, suppress_health_check=[HealthCheck.function_scoped_fixture, HealthCheck.too_slow])
 
 
 @settings(max_examples=25, **COMMON)
