@@ -27,7 +27,8 @@ def test_cfg1(cuda):
     _check(cuda, W.cfg1_decode(), "cfg1")
 
 
-@pytest.mark.parametrize("hq,hkv,d", [(16, 8, 128), (32, 8, 128), (14, 2, 64), (4, 1, 128), (7, 1, 64), (8, 1, 128), (2, 2, 64)])
+@pytest.mark.parametrize("hq,hkv,d", [(16, 8, 128), (32, 8, 128), (14, 2, 64), (4, 1, 128), (7, 1, 64), (8, 1, 128), (2, 2, 64),
+                                      (40, 8, 128), (12, 2, 128), (6, 2, 64)])
 def test_geometries(cuda, hq, hkv, d):
     case = W.make_decode_case(11, 6, 1, 1500, hq, hkv, d,
                               context_lens=[1, 255, 256, 257, 1024, 1500])
