@@ -240,7 +240,9 @@ NVLLM_API int nvllm_decode_step_inputs(const void* staged, int64_t tokens_off, i
  *   the caller gathers the handles of all ranks (rank order) by its own means;
  *   nvllm_ar_connect(all_handles)  maps every peer's area.
  * nvllm_ar_allreduce(in, out, n_elems, stream) then launches one kernel; every rank must make the
- * same sequence of calls with the same n_elems.  in == out is allowed; both 16-byte aligned;
+ * same sequence of calls with the same n_elems, and a rank's calls must execute one after the
+ * other (one stream, or otherwise serialised: the staging buffers belong to one call at a
+ * time).  in == out is allowed; both 16-byte aligned;
  * n_elems * 2 <= max_bytes.  All ranks get bit-identical sums (fp32 accumulation in rank order).
  * No allocation, synchronisation or host read in the call: legal during stream capture, and a
  * captured graph can be replayed (call counts live in device memory).  A peer that does not
