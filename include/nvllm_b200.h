@@ -19,6 +19,10 @@
  *   - Return value: 0 = kernels launched; a negative NVLLM_E_* code = the arguments were
  *     rejected on the host before any launch.  `nvllm_last_error()` then holds a message.
  *     No C++ exception crosses this boundary.
+ *   - Threads: one host thread per device at a time.  The first call of an entry point on a
+ *     device fills small per-device caches (kernel attributes, the status word's address, the SM
+ *     count) without locking; two host threads making a device's first calls at the same moment
+ *     would race.  Separate processes, one per GPU, need no care.
  *   - Problems that only the device can see (a slot or block id outside the cache) never
  *     trap: the offending access is skipped and a bit is set in a device status word that
  *     `nvllm_read_status()` returns.
@@ -79,11 +83,15 @@ NVLLM_API int nvllm_store_kvcache(const void* key, int64_t key_row_stride,
  * q/out: [batch, Hq, D] with unit inner strides and the given row (per sequence) strides.
  * block_tables: [batch, max_blocks] int32 with row stride bt_row_stride; only the first
  * ceil(ctx_b/256) entries of a row are read.  ctx_b == 0 gives a zero output row and
- * touches no cache memory.  Long contexts are cut into chunks handled by separate thread
- * blocks (split-KV) whose fp32 partial results go through `workspace` and are merged by a
- * second kernel; `workspace` must hold nvllm_decode_workspace_bytes(...) bytes for the
- * same (batch, max_blocks, Hq, Hkv, D) and is scratch (no state is kept between calls).
- * Supported: D in {64,128}; Hq % Hkv == 0; G <= 8.
+ * touches no cache memory.  One launch: the cached tokens of the whole batch are dealt out in
+ * equal shares to two thread blocks per SM, whatever the individual lengths are; a sequence
+ * whose tokens fall into several shares gets fp32 partial results in `workspace`, and the
+ * thread block that delivers the last of them merges them (no second kernel).
+ * `workspace`: nvllm_decode_workspace_bytes(...) bytes for the same (batch, Hq, Hkv, D),
+ * 16-byte aligned.  Its first 64 KiB are arrival counters: ZERO-FILL THE WORKSPACE ONCE before
+ * its first use; every completed call leaves the counters at zero again, so one workspace can
+ * serve all later calls, of any geometry, that do not overlap on the GPU.
+ * Supported: D in {64,128}; Hq % Hkv == 0; G <= 8; batch * Hkv <= 16384.
  */
 NVLLM_API int nvllm_decode_paged(const void* q, int64_t q_row_stride,
                        const void* k_cache, const void* v_cache,
@@ -94,17 +102,48 @@ NVLLM_API int nvllm_decode_paged(const void* q, int64_t q_row_stride,
                        float scale, int64_t num_blocks,
                        void* workspace, int64_t workspace_bytes, void* stream);
 
-/* Bytes of scratch nvllm_decode_paged needs for this geometry (0 if no split is used).
- * Negative NVLLM_E_* on unsupported geometry.  Pure host arithmetic.
+/*
+ * One decode step of the attention layer in one launch: store_kvcache of the new token of every
+ * sequence followed by the paged decode, i.e. nanovllm/layers/attention.py:65-66 and :74-77
+ * together.  key/value: [batch, Hkv, D] rows of the token being decoded (row strides given;
+ * value may be a strided view of the fused qkv activation); slot_mapping[b] is the cache slot of
+ * that token, which the model runner sets to the slot of position ctx_b - 1
+ * (nanovllm/engine/model_runner.py:225-229).  The thread block that streams position ctx_b - 1
+ * takes the row from key/value instead of the cache and writes it to the cache on the way, so
+ * the cache ends up exactly as store_kvcache would leave it and the output is the same as
+ * nvllm_store_kvcache followed by nvllm_decode_paged.  Rules that differ from the two separate
+ * calls: slot_mapping[b] < 0 stores nothing (the row is read from the cache as it is); a
+ * slot_mapping[b] >= 0 that is not the slot of position ctx_b - 1 is flagged
+ * NVLLM_STATUS_BAD_SLOT and not stored; rows with ctx_b == 0 (the padding rows of a captured
+ * batch) store nothing, where the reference scatters them to slot_mapping[b].
+ * Everything else as nvllm_decode_paged (same workspace, same limits).
+ */
+NVLLM_API int nvllm_decode_step(const void* q, int64_t q_row_stride,
+                      const void* key, int64_t key_row_stride,
+                      const void* value, int64_t value_row_stride,
+                      const int32_t* slot_mapping,
+                      void* k_cache, void* v_cache,
+                      const int32_t* context_lens,
+                      const int32_t* block_tables, int64_t bt_row_stride, int32_t max_blocks,
+                      void* out, int64_t out_row_stride,
+                      int32_t batch, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                      float scale, int64_t num_blocks,
+                      void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Bytes of workspace nvllm_decode_paged / nvllm_decode_step need for this geometry (0 for an
+ * empty batch): the counter area plus one partial per (share, sequence) piece, sized for the
+ * largest launch the library makes on any device.  Negative NVLLM_E_* on unsupported geometry.
+ * Pure host arithmetic, no device needed.
  * No counterpart in the reference: flash-attn allocates its split-KV scratch internally. */
 NVLLM_API int64_t nvllm_decode_workspace_bytes(int32_t batch, int32_t max_blocks,
                                      int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim);
 
-/* The split-KV plan the library uses for this geometry: tokens per chunk and the maximum
- * number of chunks per sequence.  Pure host arithmetic, exposed for tests and reports. */
+/* How the library cuts this geometry: tokens per work unit, and the number of thread blocks a
+ * launch uses on the current device (two per SM rounded down to a multiple of Hkv; the sizing
+ * cap when no device is usable).  Exposed for tests and reports. */
 NVLLM_API int nvllm_decode_plan(int32_t batch, int32_t max_blocks, int32_t num_q_heads,
                       int32_t num_kv_heads, int32_t head_dim,
-                      int32_t* chunk_tokens, int32_t* max_splits);
+                      int32_t* unit_tokens, int32_t* thread_blocks);
 
 /* Size of the scratch array built into the library for nvllm_decode_paged_static. */
 #define NVLLM_DECODE_STATIC_SCRATCH_BYTES (32ll << 20)
@@ -119,20 +158,22 @@ NVLLM_API int nvllm_decode_plan(int32_t batch, int32_t max_blocks, int32_t num_q
  * binding that only forwards pointers it received and owns no allocator.  Inputs and the
  * output are still the caller's buffers; only the split-KV partials move into the library.
  *
- * Same arguments and results as nvllm_decode_paged minus the workspace pair.  The partials go
- * to a 32 MiB (NVLLM_DECODE_STATIC_SCRATCH_BYTES) array that is part of the library image, so
- * every GPU whose context loads the library carries those 32 MiB until the process exits.
- * The call never allocates or frees anything.  Limits and rules:
+ * Same arguments and results as nvllm_decode_paged minus the workspace pair.  The counters and
+ * partials go to a 32 MiB (NVLLM_DECODE_STATIC_SCRATCH_BYTES) array that is part of the library
+ * image, so every GPU whose context loads the library carries those 32 MiB until the process
+ * exits.  The call never allocates or frees anything.  Limits and rules:
  *   - a geometry whose nvllm_decode_workspace_bytes() exceeds the array is refused with
- *     NVLLM_E_WORKSPACE before anything is launched (e.g. batch 512 with 32 query heads and
- *     4 splits); use the workspace variant for those;
+ *     NVLLM_E_WORKSPACE before anything is launched (e.g. batch 2048 with 64 query heads); use
+ *     the workspace variant for those;
  *   - the first call on each device looks up the array's device address (with that device
  *     current); make that first call outside stream capture;
  *   - all calls on a device share the one array, which still holds whatever the previous
- *     call left there.  The kernels never read a value they did not write in the same call,
- *     so nothing needs clearing; but two calls whose kernels may run at the same time on one
- *     GPU (different streams, or graphs replayed concurrently) would overwrite each other's
- *     partials — keep calls to this entry point ordered on a device.
+ *     call left there.  Only the arrival counters at its head have to start at zero: they do
+ *     when the library is loaded, and the thread block that merges a sequence puts its counter
+ *     back to zero, so a completed call leaves them cleared.  Partials are written before they
+ *     are read within one call.  Two calls whose kernels may run at the same time on one GPU
+ *     (different streams, or graphs replayed concurrently) would disturb each other's counters
+ *     and partials — keep calls to this entry point ordered on a device.
  */
 NVLLM_API int nvllm_decode_paged_static(const void* q, int64_t q_row_stride,
                               const void* k_cache, const void* v_cache,

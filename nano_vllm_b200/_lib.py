@@ -21,6 +21,9 @@ SIGNATURES = {
     "nvllm_decode_paged": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32,
                                      c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_float, c_int64,
                                      c_void_p, c_int64, c_void_p]),
+    "nvllm_decode_step": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                                    c_void_p, c_void_p, c_int64, c_int32, c_void_p, c_int64, c_int32, c_int32, c_int32,
+                                    c_int32, c_float, c_int64, c_void_p, c_int64, c_void_p]),
     "nvllm_decode_paged_static": (c_int32, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int32,
                                             c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_float, c_int64,
                                             c_void_p]),
@@ -99,9 +102,10 @@ def read_status() -> int:
 
 
 def decode_plan(batch: int, max_blocks: int, hq: int, hkv: int, d: int) -> tuple[int, int]:
-    chunk, splits = c_int32(0), c_int32(0)
-    check(load().nvllm_decode_plan(batch, max_blocks, hq, hkv, d, ctypes.byref(chunk), ctypes.byref(splits)))
-    return chunk.value, splits.value
+    """(tokens per work unit, thread blocks per launch on the current device)."""
+    unit, ctas = c_int32(0), c_int32(0)
+    check(load().nvllm_decode_plan(batch, max_blocks, hq, hkv, d, ctypes.byref(unit), ctypes.byref(ctas)))
+    return unit.value, ctas.value
 
 
 def decode_workspace_bytes(batch: int, max_blocks: int, hq: int, hkv: int, d: int) -> int:

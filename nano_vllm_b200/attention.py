@@ -46,8 +46,10 @@ def _require_i32(name: str, t: torch.Tensor) -> None:
 
 
 # ---- decode scratch ---------------------------------------------------------------------
-# One buffer per device, grown on demand.  Outgrown buffers are kept alive because CUDA
-# graphs captured earlier still hold their addresses.
+# One buffer per device, grown on demand and zero-filled when it is made: its head holds the
+# arrival counters of the decode kernel, which must start at zero and which every completed
+# call leaves at zero.  Outgrown buffers are kept alive because CUDA graphs captured earlier
+# still hold their addresses.
 _workspaces: dict[int, torch.Tensor] = {}
 _retired: list[torch.Tensor] = []
 
@@ -60,7 +62,7 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor | None:
     if ws is None or ws.numel() < nbytes:
         if ws is not None:
             _retired.append(ws)
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[idx] = ws
     return ws
 
@@ -125,12 +127,53 @@ def decode_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     return out
 
 
+def decode_step(q: torch.Tensor, key: torch.Tensor, value: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                slot_mapping: torch.Tensor, context_lens: torch.Tensor, block_tables: torch.Tensor, scale: float,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """``store_kvcache(key, value, k_cache, v_cache, slot_mapping)`` followed by ``decode_paged`` as
+    ONE launch: what nanovllm/layers/attention.py:65-66 and :74-77 do for a decode batch.  The
+    thread block that streams a sequence's newest position takes that row from ``key`` /
+    ``value`` and writes it to the cache on the way.  ``slot_mapping[b]`` must be the slot of
+    position ``context_lens[b] - 1`` (what the model runner passes) or negative (nothing stored);
+    rows with ``context_lens[b] == 0`` store nothing.  q/out ``[B, Hq, D]``, key/value ``[B, Hkv, D]``.
+    """
+    B, Hq, D = q.shape
+    Hkv = k_cache.shape[-2]
+    for name, t in (("q", q), ("key", key), ("value", value), ("k_cache", k_cache), ("v_cache", v_cache)):
+        _require_cuda_bf16(name, t)
+    _require_i32("slot_mapping", slot_mapping)
+    _require_i32("context_lens", context_lens)
+    _require_i32("block_tables", block_tables)
+    assert q.stride(-1) == 1 and q.stride(1) == D
+    assert key.shape == (B, Hkv, D) and value.shape == (B, Hkv, D)
+    assert key.stride(-1) == 1 and value.stride(-1) == 1 and key.stride(1) == D and value.stride(1) == D
+    assert k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert block_tables.dim() == 2 and block_tables.shape[0] == B and context_lens.numel() == B
+    assert slot_mapping.numel() == B
+    if out is None:
+        out = torch.empty((B, Hq, D), dtype=q.dtype, device=q.device)
+    assert out.stride(-1) == 1 and out.stride(1) == D
+    max_blocks = block_tables.shape[1]
+    num_blocks = k_cache.numel() // (BLOCK_SIZE * Hkv * D)
+    if B == 0:
+        return out
+    with torch.cuda.device(q.device):
+        ws = _workspace(q.device, _lib.decode_workspace_bytes(B, max_blocks, Hq, Hkv, D))
+        _lib.check(_lib.load().nvllm_decode_step(
+            q.data_ptr(), q.stride(0), key.data_ptr(), key.stride(0), value.data_ptr(), value.stride(0),
+            slot_mapping.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+            context_lens.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), max_blocks,
+            out.data_ptr(), out.stride(0), B, Hq, Hkv, D, float(scale), num_blocks,
+            ws.data_ptr(), ws.numel(), _stream(q)))
+    return out
+
+
 def decode_paged_static(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, context_lens: torch.Tensor,
                         block_tables: torch.Tensor, scale: float, out: torch.Tensor) -> torch.Tensor:
     """``decode_paged`` for hosts that may not allocate device memory while serving (all free
     HBM already belongs to the KV cache, or an allocation's implicit synchronisation is not
-    acceptable): the split-KV partials go to a 32 MiB array inside the library instead of a
-    torch-allocated workspace, and ``out`` must be supplied, so this call allocates nothing.
+    acceptable): the arrival counters and partials go to a 32 MiB array inside the library instead
+    of a torch-allocated workspace, and ``out`` must be supplied, so this call allocates nothing.
     Raises ``NvllmError`` (NVLLM_E_WORKSPACE) for geometries whose scratch exceeds the array.
     Calls on one device share that array: keep them ordered on the GPU.  Make the first call
     on a device outside CUDA graph capture.  No counterpart in nano-vllm."""

@@ -44,6 +44,24 @@ int* status_word() {
   return g_status_addr[dev];
 }
 
+int num_sms() {
+  static std::atomic<int> cached[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return 0;
+    }
+    cached[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 bool pdl_enabled() {
@@ -78,7 +96,7 @@ int nvllm_read_status(int32_t* host_out) {
   return NVLLM_OK;
 }
 
-int nvllm_abi_version(void) { return 1; }
+int nvllm_abi_version(void) { return 2; }
 
 int64_t nvllm_launch_count(void) { return nvllm::g_launches.load(std::memory_order_relaxed); }
 

@@ -29,14 +29,11 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 bool pdl_enabled();
 
 constexpr int kBlockSize = NVLLM_BLOCK_SIZE;
-constexpr int kNumSMs = 148;
 
-// Split-KV plan for decode: pure function of host-visible geometry.
-struct DecodePlan {
-  int chunk_tokens;  // tokens handled by one thread block (multiple of 64)
-  int max_splits;    // ceil(max_blocks*256 / chunk_tokens)
-};
-DecodePlan make_decode_plan(int batch, int max_blocks, int hq, int hkv, int d);
+// Multiprocessor count of the current device (queried once per device); 0 when no device is
+// usable.  Launch geometry that aims at "k blocks per SM" is derived from this, never from a
+// constant of one chip.
+int num_sms();
 
 // ---- device side -----------------------------------------------------------------------
 #ifdef __CUDACC__
@@ -60,6 +57,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 // asks for the whole aligned 128-byte line, which the neighbouring lanes' copies need anyway.
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, int src_bytes) {
   asm volatile("cp.async.cg.shared.global.L2::128B [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void st_shared16(uint32_t dst, const uint4& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>

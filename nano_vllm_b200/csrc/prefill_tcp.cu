@@ -455,14 +455,12 @@ template <int D>
 static int launch_prefill_tcp_t(const PrefillParams& p_in, int64_t total_q, int64_t total_k, cudaStream_t stream) {
   using G = tcp::Geo<D>;
   static bool attr_done[64] = {false};
-  static int num_sms[64] = {0};
   static std::atomic<unsigned> launch_seq{0};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return fail(NVLLM_E_NO_DEVICE, "prefill: device index %d out of range", dev);
   if (!attr_done[dev]) {
     cudaError_t e = cudaFuncSetAttribute(prefill_tcp_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM);
-    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&num_sms[dev], cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return fail(NVLLM_E_CUDA, "prefill (persistent): set-up failed: %s", cudaGetErrorString(e));
     attr_done[dev] = true;
   }
@@ -488,7 +486,8 @@ static int launch_prefill_tcp_t(const PrefillParams& p_in, int64_t total_q, int6
   }
   // an upper bound of the work items known to the host: no more blocks than that
   const int64_t max_items = static_cast<int64_t>((p.max_seqlen_q + bmt - 1) / bmt) * (p.hq / pack) * p.batch;
-  int grid = 2 * num_sms[dev];
+  int grid = 2 * num_sms();
+  if (grid <= 0) return fail(NVLLM_E_NO_DEVICE, "prefill: no CUDA device is usable");
   if (max_items < grid) grid = static_cast<int>(max_items);
   // the two head_dim instantiations share the counter array: give each its own half
   const int slot = static_cast<int>(launch_seq.fetch_add(1) % (tcp::NUM_SLOTS / 2)) + (D == 64 ? tcp::NUM_SLOTS / 2 : 0);

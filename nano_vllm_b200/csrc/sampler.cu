@@ -243,9 +243,11 @@ extern "C" int nvllm_sample_tokens(const void* logits, int32_t logits_are_fp32, 
   p.vocab = vocab;
   // rows whose start is not 16-byte aligned take the element-wise path inside the kernel.
   // Blocks per row: as many (1, 2, 4, 8) as keep the grid within one resident wave of
-  // 148 SMs x 8 blocks, and no more than the row has work for.
+  // 8 blocks on every SM of this device, and no more than the row has work for.
+  const int sms = num_sms();
+  if (sms <= 0) return fail(NVLLM_E_NO_DEVICE, "sample_tokens: no CUDA device is usable");
   int csize = 8;
-  while (csize > 1 && (static_cast<int64_t>(batch) * csize > kNumSMs * (NVLLM_SAMPLER_MINBLOCKS > 4 ? NVLLM_SAMPLER_MINBLOCKS : 8) || vocab < csize * 256 * 8)) csize >>= 1;
+  while (csize > 1 && (static_cast<int64_t>(batch) * csize > static_cast<int64_t>(sms) * (NVLLM_SAMPLER_MINBLOCKS > 4 ? NVLLM_SAMPLER_MINBLOCKS : 8) || vocab < csize * 256 * 8)) csize >>= 1;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(static_cast<unsigned>(batch) * csize, 1, 1);
   cfg.blockDim = dim3(256, 1, 1);
