@@ -51,10 +51,15 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     cmd = [_nvcc(), *NVCC_FLAGS]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", str(LIB_PATH), *map(str, sources())]
+    # compile to a private name and rename: a process that loads the library while another one
+    # builds it sees either the old file or the complete new one, never a half-written file
+    tmp = LIB_PATH.with_name(f".{LIB_PATH.name}.{os.getpid()}.tmp")
+    cmd += ["-o", str(tmp), *map(str, sources())]
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
+        tmp.unlink(missing_ok=True)
         raise RuntimeError("nvcc failed:\n" + " ".join(cmd) + "\n" + proc.stdout + proc.stderr)
+    os.replace(tmp, LIB_PATH)
     if verbose:
         sys.stderr.write(proc.stderr)
     return LIB_PATH

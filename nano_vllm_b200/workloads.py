@@ -181,7 +181,7 @@ def make_prefill_case(seed: int, batch: int, len_lo: int, len_hi: int, hq: int, 
                        float(d) ** -0.5)
 
 
-# ---- the five BASELINE.json configurations -------------------------------------------------
+# ---- the benchmark configurations ----------------------------------------------------------
 
 QWEN3_06B = dict(hq=16, hkv=8, d=128)   # models/qwen3_06b.txt:10-20 of the reference
 QWEN3_8B = dict(hq=32, hkv=8, d=128)

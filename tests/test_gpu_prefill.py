@@ -32,7 +32,7 @@ def _check(cuda, case, what):
 
 
 def test_cfg2(cuda):
-    """BASELINE config 2: 64 prompts in [100,1024], every 4th shares 1-3 cached blocks."""
+    """The prefill configuration at full size: 64 prompts in [100,1024], every 4th shares 1-3 cached blocks."""
     case = W.cfg2_prefill()
     assert case.block_tables is not None and int(case.cu_seqlens_k[-1]) > int(case.cu_seqlens_q[-1])
     _check(cuda, case, "cfg2")
