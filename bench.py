@@ -75,6 +75,8 @@ def parse_args():
                     choices=["prefill", "prefill_long", "prefill_d64", "store", "decode", "decode_tp8", "decode_long", "sampler",
                              "allreduce"],
                     help="time only this kernel and print its line (profiling aid; allreduce runs under torchrun)")
+    ap.add_argument("--ar-protocol", type=int, default=0, choices=[0, 1, 2, 3],
+                    help="with --kernel allreduce: force a protocol (0 automatic, 1 cells, 2 one shot, 3 two shots)")
     ap.add_argument("--with-flash-attn", action="store_true",
                     help="with --kernel: also time the library kernels the reference calls (flash-attn, Triton "
                          "store) on the same inputs, if they are importable")
@@ -727,6 +729,7 @@ def run_allreduce(args):
         return g, calls
 
     ar = PeerAllReduce(rank, world, 8 << 20, wait_ms=20000)
+    ar.force_protocol(args.ar_protocol)
     for rows, hidden in ((16, 1024), (256, 1024), (64, 4096), (256, 4096), (512, 4096)):
         x = (torch.randn(rows, hidden, generator=torch.Generator().manual_seed(rank)) * 0.5).to(torch.bfloat16).cuda()
         y1, y2 = x.clone(), x.clone()
@@ -735,7 +738,7 @@ def run_allreduce(args):
         torch.cuda.synchronize()
         scratch = x.clone()
         line = {"kernel": "allreduce", "bytes": x.numel() * 2, "shape": [rows, hidden], "world": world,
-                "max_abs_diff_vs_nccl": float((y1.float() - y2.float()).abs().max())}
+                "protocol": ar.protocol(x.numel() * 2), "max_abs_diff_vs_nccl": float((y1.float() - y2.float()).abs().max())}
         line["peer_us"] = round(timed(lambda: ar.all_reduce(scratch), iters), 2)
         line["nccl_us"] = round(timed(lambda: dist.all_reduce(scratch), iters), 2)
         scratch.copy_(x)

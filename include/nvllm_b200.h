@@ -276,7 +276,7 @@ NVLLM_API int nvllm_decode_step_inputs(const void* staged, int64_t tokens_off, i
  * GPU.  Replaces dist.all_reduce in RowParallelLinear.forward (nanovllm/layers/linear.py:195-199)
  * for tensors up to `max_bytes`.  Set-up, once per process and device, outside stream capture:
  *   nvllm_ar_init(rank, world, max_bytes, handle_out)  allocates this rank's flag + staging area
- *       (8 KB + 4 * max_bytes of device memory) and writes its CUDA IPC handle
+ *       (8 KB + 6 * max_bytes of device memory) and writes its CUDA IPC handle
  *       (nvllm_ar_handle_bytes() bytes) to handle_out;
  *   the caller gathers the handles of all ranks (rank order) by its own means;
  *   nvllm_ar_connect(all_handles)  maps every peer's area.
@@ -285,6 +285,13 @@ NVLLM_API int nvllm_decode_step_inputs(const void* staged, int64_t tokens_off, i
  * other (one stream, or otherwise serialised: the staging buffers belong to one call at a
  * time).  in == out is allowed; both 16-byte aligned;
  * n_elems * 2 <= max_bytes.  All ranks get bit-identical sums (fp32 accumulation in rank order).
+ * The call picks one of three protocols from (n_elems, world, max_bytes) alone, the same on every
+ * rank: flagged 16-byte cells pushed to every peer (small tensors: one NVLink crossing of
+ * latency), staging + flags with every rank pulling all peers' tensors (one shot), or, at more
+ * than two ranks, reduce-scatter + all-gather over pushed slices (two shots: a rank moves
+ * 2 (world-1)/world of the tensor instead of world-1 of it).  nvllm_ar_protocol() reports the
+ * choice (1 cells, 2 one shot, 3 two shots); nvllm_ar_set_protocol() forces one where it applies
+ * (0 = automatic; measurement aid; every rank must set the same).
  * No allocation, synchronisation or host read in the call: legal during stream capture, and a
  * captured graph can be replayed (call counts live in device memory).  A peer that does not
  * arrive within ~1 s of SM clocks sets NVLLM_STATUS_TIMEOUT; that call's output is invalid and
@@ -298,17 +305,21 @@ NVLLM_API int64_t nvllm_ar_max_bytes(void); /* 0 until connected */
  * that run loosely coupled (one may be seconds behind while it compiles or captures) need more. */
 NVLLM_API int nvllm_ar_set_wait_ms(int64_t ms);
 NVLLM_API int nvllm_ar_allreduce(const void* in, void* out, int64_t n_elems, void* stream);
+NVLLM_API int nvllm_ar_set_protocol(int32_t protocol);
+/* Pure host arithmetic; no device needed. */
+NVLLM_API int nvllm_ar_protocol(int64_t n_elems, int32_t world, int64_t max_bytes, int32_t forced);
 NVLLM_API int nvllm_ar_shutdown(void);
 /* The same hand-shake and arithmetic with all `world` ranks emulated by ONE cooperative launch on
  * the current device (inputs[r], outputs[r]: rank r's tensors; scratch: zero-filled before the
  * first call, nvllm_ar_emulated_scratch_bytes(world, max_bytes) bytes, kept between calls).  For
  * testing the protocol where fewer GPUs than ranks are at hand; absent_rank >= 0 makes that rank
  * stay away, so that the others' bounded waits run out (~1 s) and report NVLLM_STATUS_TIMEOUT
- * without any fault; -1 = all present.  No counterpart in the reference. */
+ * without any fault; -1 = all present.  protocol: as nvllm_ar_set_protocol.  No counterpart in
+ * the reference. */
 NVLLM_API int64_t nvllm_ar_emulated_scratch_bytes(int32_t world, int64_t max_bytes);
 NVLLM_API int nvllm_ar_allreduce_emulated(int32_t world, const void* const* inputs, void* const* outputs,
                                 int64_t n_elems, void* scratch, int64_t scratch_bytes, int64_t max_bytes,
-                                int32_t absent_rank, void* stream);
+                                int32_t absent_rank, int32_t protocol, void* stream);
 
 /* Known-answer check of the tensor-core building blocks the prefill kernel is made of
  * (TMA swizzled loads, shared-memory and instruction descriptors, TMEM loads and stores):

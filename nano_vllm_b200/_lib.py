@@ -45,10 +45,12 @@ SIGNATURES = {
     "nvllm_ar_max_bytes": (c_int64, []),
     "nvllm_ar_set_wait_ms": (c_int32, [c_int64]),
     "nvllm_ar_allreduce": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p]),
+    "nvllm_ar_set_protocol": (c_int32, [c_int32]),
+    "nvllm_ar_protocol": (c_int32, [c_int64, c_int32, c_int64, c_int32]),
     "nvllm_ar_shutdown": (c_int32, []),
     "nvllm_ar_emulated_scratch_bytes": (c_int64, [c_int32, c_int64]),
     "nvllm_ar_allreduce_emulated": (c_int32, [c_int32, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int32,
-                                              c_void_p]),
+                                              c_int32, c_void_p]),
     "nvllm_selftest_umma": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvllm_selftest_wait_expiry": (c_int32, [c_void_p, c_void_p]),
     "nvllm_last_error": (c_char_p, []),

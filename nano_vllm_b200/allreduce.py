@@ -25,17 +25,23 @@ def gather_handles(handle: bytes, rank: int, world: int, dist=None) -> bytes:
     return b"".join(parts)
 
 
+PROTOCOLS = {0: "auto", 1: "cells", 2: "one-shot", 3: "two-shot"}
+
+
+def protocol_for(nbytes: int, world: int, max_bytes: int, forced: int = 0) -> str:
+    """The protocol the kernel picks for a bf16 tensor of ``nbytes`` (pure host arithmetic in the
+    library: the same function the kernel evaluates)."""
+    return PROTOCOLS[_lib.load().nvllm_ar_protocol(nbytes // 2, world, max_bytes, forced)]
+
+
 def prefer_peer_kernel(nbytes: int, world: int, max_bytes: int) -> bool:
-    """Whether the peer-memory kernel is expected to beat the library collective for a tensor of
-    ``nbytes``: always at two ranks (measured up to 4 MiB); at more ranks only while the
-    flagged-cell protocol applies (2 x nbytes x world <= max_bytes) and a rank pushes at most
-    8 MiB in total (2 x nbytes to each peer) -- an estimate from the two-rank measurements, larger
-    worlds were not measured."""
+    """Whether the peer-memory kernel is used instead of the library collective for a tensor of
+    ``nbytes``: whenever it fits the staging buffers and is decode-sized (at most 4 MiB: the
+    sizes on which the kernel was timed next to NCCL at 2, 4 and 8 ranks); prefill-sized tensors
+    are bandwidth-bound and stay with the library."""
     if nbytes <= 0 or (nbytes + 15) // 16 * 16 > max_bytes:
         return False
-    if world == 2:
-        return True
-    return 2 * nbytes * world <= max_bytes and 2 * nbytes * (world - 1) <= (8 << 20)
+    return nbytes <= (4 << 20)
 
 
 class PeerAllReduce:
@@ -51,7 +57,7 @@ class PeerAllReduce:
         _lib.check(lib.nvllm_ar_connect(handles))
         if wait_ms is not None:
             _lib.check(lib.nvllm_ar_set_wait_ms(wait_ms))
-        self.rank, self.world, self.max_bytes = rank, world, max_bytes
+        self.rank, self.world, self.max_bytes, self.forced = rank, world, max_bytes, 0
 
     def fits(self, x: torch.Tensor) -> bool:
         return (x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.data_ptr() % 16 == 0
@@ -60,6 +66,14 @@ class PeerAllReduce:
     def preferred(self, x: torch.Tensor) -> bool:
         """``fits(x)`` and ``prefer_peer_kernel`` for its size."""
         return self.fits(x) and prefer_peer_kernel(x.numel() * 2, self.world, self.max_bytes)
+
+    def protocol(self, nbytes: int) -> str:
+        return protocol_for(nbytes, self.world, self.max_bytes, self.forced)
+
+    def force_protocol(self, protocol: int) -> None:
+        """0 automatic, 1 cells, 2 one shot, 3 two shots; every rank must set the same."""
+        _lib.check(_lib.load().nvllm_ar_set_protocol(protocol))
+        self.forced = protocol
 
     def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
         if not self.fits(x):
@@ -75,15 +89,16 @@ class PeerAllReduce:
 
 
 def all_reduce_emulated(inputs: list[torch.Tensor], scratch: torch.Tensor, max_bytes: int,
-                        absent_rank: int = -1) -> list[torch.Tensor]:
+                        absent_rank: int = -1, protocol: int = 0) -> list[torch.Tensor]:
     """All ranks' reductions in one cooperative launch on one device (test aid): returns one
-    output per rank.  ``scratch``: uint8, zero-filled before its first use, kept between calls."""
+    output per rank.  ``scratch``: uint8, zero-filled before its first use, kept between calls.
+    ``protocol``: 0 automatic, 1 cells, 2 one shot, 3 two shots."""
     world = len(inputs)
     outs = [torch.empty_like(x) for x in inputs]
     arr = ctypes.c_void_p * world
     with torch.cuda.device(inputs[0].device):
         _lib.check(_lib.load().nvllm_ar_allreduce_emulated(
             world, arr(*[x.data_ptr() for x in inputs]), arr(*[o.data_ptr() for o in outs]), inputs[0].numel(),
-            scratch.data_ptr(), scratch.numel(), max_bytes, absent_rank,
+            scratch.data_ptr(), scratch.numel(), max_bytes, absent_rank, protocol,
             torch.cuda.current_stream(inputs[0].device).cuda_stream))
     return outs

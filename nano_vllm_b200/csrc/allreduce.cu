@@ -6,9 +6,10 @@
 // [batch, hidden] bf16 tensor of 0.5-2 MiB, i.e. latency-bound.  Here every rank owns one device
 // allocation that all its peers map through CUDA IPC:
 //
-//     [ flags: kMaxBlocks x kMaxRanks u32 | call counts | staging 0 | staging 1 | cells 0 | cells 1 ]
+//     [ flags: kMaxBlocks x kMaxRanks u32 | call counts | staging 0 | staging 1 | cells 0 | cells 1 |
+//       result 0 | result 1 ]
 //
-// Two protocols, chosen by size (the same choice on every rank).
+// Three protocols, chosen by size and world (the same choice on every rank).
 //
 // SMALL tensors (2 x bytes x world <= max_bytes): flagged cells, in the manner of NCCL's
 // low-latency protocol.  A cell is 16 bytes: 8 bytes of data and the call count twice
@@ -18,18 +19,31 @@
 // until the cells of every peer carry this call's count, and sums in rank order.  No fence, no
 // separate flag round trip, no block-wide barrier: one NVLink crossing of latency.
 //
-// LARGER tensors: staging + flags.
+// LARGER tensors, one shot: staging + flags.
 //
 // One call = one kernel on every rank, same grid everywhere.  Block b of rank r
 //   1. copies its slice of the input into r's staging buffer (e & 1), e = the block's call count,
-//   2. publishes e into flag (b, r) of every peer (st.release.sys through the peer mapping),
-//   3. waits until its own flags (b, p) have reached e for every peer p (ld.acquire.sys; bounded
+//   2. publishes 2e into flag (b, r) of every peer (st.release.sys through the peer mapping),
+//   3. waits until its own flags (b, p) have reached 2e for every peer p (ld.acquire.sys; bounded
 //      by a clock limit, after which the status word gets NVLLM_STATUS_TIMEOUT, a latch in the
 //      allocation makes later calls give up at once, and the block carries on without hanging),
 //   4. sums slice b of every rank's staging buffer in rank order, in fp32, and writes bf16.
 // Every rank adds the same numbers in the same order, so all ranks hold bit-identical results.
 // Two staging buffers used in turn need no closing barrier: a peer cannot reach call e+2 (which
 // overwrites buffer e & 1) before this rank has published e+1, which it does after reading.
+//
+// LARGER tensors at more than two ranks, two shots (reduce-scatter, then all-gather): one shot
+// makes every rank pull world-1 whole tensors; here a rank moves 2 (world-1)/world of one.  The
+// tensor is cut into `world` slices, slice j owned by rank j.  Block b of rank r
+//   1. pushes its part of slice j of the input straight into rank j's staging buffer, region
+//      [source r], for every peer j; publishes 2e-1 to flag (b, r) of every peer; waits for 2e-1,
+//   2. sums its part of slice r (own input + the world-1 regions of its staging buffer) in rank
+//      order in fp32, writes the bf16 result to `out` and pushes it into the result buffer (e & 1)
+//      of every peer; publishes 2e; waits for 2e,
+//   3. copies the other slices' results from its own result buffer to `out`.
+// A slice is summed by exactly one rank, so all ranks hold the same bits.  The flag values of the
+// two staging protocols interleave (2e-1 < 2e < 2(e+1)-1), so calls of either kind can follow
+// each other, and the two-buffer argument above covers both areas.
 // All accesses to peer memory are plain 16-byte loads and stores issued by each thread itself:
 // no bulk-copy engine and no switch-side broadcast or reduction object is involved.  Flags and
 // call counts live in device memory, so a captured graph replays correctly.
@@ -52,6 +66,11 @@ constexpr int64_t kBrokenOff = kEpochOff + kMaxBlocks * 4;     // u32 latch
 constexpr int64_t kCellEpochOff = kBrokenOff + 64;             // u32[kMaxBlocks], call counts of the cell protocol
 constexpr int64_t kHeaderBytes = 8192;
 static_assert(kCellEpochOff + kMaxBlocks * 4 <= kHeaderBytes, "header");
+constexpr int kAreas = 6;  // staging 0/1, cells 0/1, result 0/1: max_bytes each
+enum Protocol { kAuto = 0, kCells = 1, kOneShot = 2, kTwoShot = 3 };
+// Above this size the flagged cells (twice the bytes on the wire, to every peer) lose against two
+// shots at more than two ranks.
+constexpr int64_t kCellsMaxBytesManyRanks = 128 << 10;
 
 struct Peers {
   unsigned char* base[kMaxRanks];
@@ -65,6 +84,7 @@ struct Params {
   int64_t stage_bytes;
   long long wait_cycles;  // a wait for a peer gives up after this many SM clocks
   int rank, world;
+  int force;  // Protocol: kAuto, or the protocol to use (measurement aid; same on every rank)
   Peers peers;
   int* status;
 };
@@ -134,11 +154,11 @@ __device__ void allreduce_block(const Params& p, int rank, int b, int nblocks) {
   // 2. publish, 3. wait (one thread per peer)
   if (tid < p.world && tid != rank) {
     uint32_t* theirs = reinterpret_cast<uint32_t*>(p.peers.base[tid]) + b * kMaxRanks + rank;
-    st_release_sys(theirs, e);
+    st_release_sys(theirs, 2 * e);
     const uint32_t* mine = reinterpret_cast<const uint32_t*>(own) + b * kMaxRanks + tid;
     if (!s_abort) {
       const long long t0 = clock64();
-      while (static_cast<int32_t>(ld_acquire_sys(mine) - e) < 0) {
+      while (static_cast<int32_t>(ld_acquire_sys(mine) - 2 * e) < 0) {
         if (clock64() - t0 > p.wait_cycles) {
           atomicOr(p.status, NVLLM_STATUS_TIMEOUT);
           *reinterpret_cast<volatile uint32_t*>(broken) = 1;  // later calls do not wait again
@@ -259,13 +279,119 @@ __device__ void allreduce_cells_block(const Params& p, int rank, int b, int nblo
   if (tid == 0) epochs[b] = e;
 }
 
-__device__ __forceinline__ bool use_cells(const Params& p) {
-  return 2 * ((p.n16 * 8 + p.tail_elems + 3) / 4 * 8) * p.world <= p.stage_bytes;
+// Two shots: the work of block `b` (of `nblocks`) on behalf of rank `rank`.  tail_elems == 0.
+__device__ void allreduce_twoshot_block(const Params& p, int rank, int b, int nblocks) {
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_abort;
+  const int tid = threadIdx.x;
+  const int w = p.world;
+  unsigned char* own = p.peers.base[rank];
+  uint32_t* epochs = reinterpret_cast<uint32_t*>(own + kEpochOff);
+  uint32_t* broken = reinterpret_cast<uint32_t*>(own + kBrokenOff);
+  if (tid == 0) {
+    s_epoch = epochs[b] + 1;
+    s_abort = *reinterpret_cast<volatile uint32_t*>(broken) != 0;
+  }
+  __syncthreads();
+  const uint32_t e = s_epoch;
+  const int64_t stage_off = kHeaderBytes + static_cast<int64_t>(e & 1) * p.stage_bytes;
+  const int64_t result_off = kHeaderBytes + (4 + static_cast<int64_t>(e & 1)) * p.stage_bytes;
+  const int64_t slice_cap = p.stage_bytes / 16 / w;  // vectors per source region of a staging buffer
+  // this block's part [lo, hi) of slice j
+  auto part = [&](int j, int64_t& s0, int64_t& lo, int64_t& hi) {
+    s0 = p.n16 * j / w;
+    const int64_t len = p.n16 * (j + 1) / w - s0;
+    lo = s0 + len * b / nblocks;
+    hi = s0 + len * (b + 1) / nblocks;
+  };
+  // publish `value` to flag (b, rank) of every peer and wait for the peers' (one thread per peer)
+  auto handshake = [&](uint32_t value) {
+    __threadfence_system();
+    __syncthreads();
+    if (tid < w && tid != rank) {
+      uint32_t* theirs = reinterpret_cast<uint32_t*>(p.peers.base[tid]) + b * kMaxRanks + rank;
+      st_release_sys(theirs, value);
+      const uint32_t* mine = reinterpret_cast<const uint32_t*>(own) + b * kMaxRanks + tid;
+      if (!s_abort) {
+        const long long t0 = clock64();
+        while (static_cast<int32_t>(ld_acquire_sys(mine) - value) < 0) {
+          if (clock64() - t0 > p.wait_cycles) {
+            atomicOr(p.status, NVLLM_STATUS_TIMEOUT);
+            *reinterpret_cast<volatile uint32_t*>(broken) = 1;  // later calls do not wait again
+            break;
+          }
+        }
+      }
+    }
+    __syncthreads();
+  };
+
+  // 1. scatter: my part of every other slice goes to its owner, region [source = rank]
+  for (int k = 1; k < w; ++k) {
+    const int j = (rank + k) % w;  // every rank starts with another peer
+    int64_t s0, lo, hi;
+    part(j, s0, lo, hi);
+    uint4* dst = reinterpret_cast<uint4*>(p.peers.base[j] + stage_off) + rank * slice_cap - s0;
+    for (int64_t v = lo + tid; v < hi; v += blockDim.x) dst[v] = p.in[v];
+  }
+  handshake(2 * e - 1);
+
+  // 2. reduce my part of my own slice in rank order; result to `out` and to every peer
+  {
+    int64_t s0, lo, hi;
+    part(rank, s0, lo, hi);
+    const uint4* stage = reinterpret_cast<const uint4*>(own + stage_off);
+    for (int64_t v = lo + tid; v < hi; v += blockDim.x) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < w; ++r) add8(acc, r == rank ? p.in[v] : ld_volatile16(stage + r * slice_cap + (v - s0)));
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
+      p.out[v] = o;
+      for (int k = 1; k < w; ++k) {
+        const int j = (rank + k) % w;
+        reinterpret_cast<uint4*>(p.peers.base[j] + result_off)[v] = o;
+      }
+    }
+  }
+  handshake(2 * e);
+
+  // 3. gather: the other owners' results are in my result buffer
+  const uint4* result = reinterpret_cast<const uint4*>(own + result_off);
+  for (int k = 1; k < w; ++k) {
+    const int j = (rank + k) % w;
+    int64_t s0, lo, hi;
+    part(j, s0, lo, hi);
+    for (int64_t v = lo + tid; v < hi; v += blockDim.x) p.out[v] = ld_volatile16(result + v);
+  }
+  if (tid == 0) epochs[b] = e;
+}
+
+// Which protocol a call uses: a pure function of (size, world, buffer size, forced choice), so
+// every rank picks the same.
+__host__ __device__ inline int pick_protocol(int64_t n16, int64_t tail_elems, int64_t stage_bytes, int world, int force) {
+  const int64_t n_elems = n16 * 8 + tail_elems;
+  const bool cells_fit = 2 * ((n_elems + 3) / 4 * 8) * world <= stage_bytes;
+  const bool twoshot_fits = world > 2 && tail_elems == 0 && (n16 + world - 1) / world <= stage_bytes / 16 / world;
+  if (force == kCells && cells_fit) return kCells;
+  if (force == kTwoShot && twoshot_fits) return kTwoShot;
+  if (force == kOneShot) return kOneShot;
+  if (cells_fit && (world == 2 || n_elems * 2 <= kCellsMaxBytesManyRanks)) return kCells;
+  if (twoshot_fits) return kTwoShot;
+  return kOneShot;
+}
+
+__device__ __forceinline__ void allreduce_dispatch(const Params& p, int rank, int b, int nblocks) {
+  const int proto = pick_protocol(p.n16, p.tail_elems, p.stage_bytes, p.world, p.force);
+  if (proto == kCells) allreduce_cells_block(p, rank, b, nblocks);
+  else if (proto == kTwoShot) allreduce_twoshot_block(p, rank, b, nblocks);
+  else allreduce_block(p, rank, b, nblocks);
 }
 
 __global__ void __launch_bounds__(kThreads) allreduce_kernel(const Params p) {
-  if (use_cells(p)) allreduce_cells_block(p, p.rank, blockIdx.x, gridDim.x);
-  else allreduce_block(p, p.rank, blockIdx.x, gridDim.x);
+  allreduce_dispatch(p, p.rank, blockIdx.x, gridDim.x);
 }
 
 // All ranks in ONE launch on one device (blockIdx.y = rank; in/out per rank): the only legal way
@@ -283,14 +409,14 @@ __global__ void __launch_bounds__(kThreads) allreduce_emulated_kernel(const EmuP
   if (rank == ep.absent_rank) return;
   p.in = ep.in[rank];
   p.out = ep.out[rank];
-  if (use_cells(p)) allreduce_cells_block(p, rank, blockIdx.x, gridDim.x);
-  else allreduce_block(p, rank, blockIdx.x, gridDim.x);
+  allreduce_dispatch(p, rank, blockIdx.x, gridDim.x);
 }
 
 // ---- host state (one per device of this process) ---------------------------------------------
 struct State {
   bool ready = false, connected = false;
   int rank = 0, world = 0;
+  int force = kAuto;
   int64_t stage_bytes = 0;
   long long wait_cycles = sm100::kWaitLimitCycles;
   unsigned char* own = nullptr;
@@ -330,7 +456,7 @@ extern "C" int nvllm_ar_init(int32_t rank, int32_t world, int64_t max_bytes, voi
     return fail(NVLLM_E_GEOMETRY, "ar_init: rank=%d world=%d invalid (2..%d ranks)", rank, world, ar::kMaxRanks);
   if (max_bytes <= 0 || max_bytes % 16) return fail(NVLLM_E_GEOMETRY, "ar_init: max_bytes must be a positive multiple of 16");
   if (!handle_out) return fail(NVLLM_E_NULL, "ar_init: NULL handle_out");
-  const size_t total = static_cast<size_t>(ar::kHeaderBytes + 4 * max_bytes);
+  const size_t total = static_cast<size_t>(ar::kHeaderBytes + ar::kAreas * max_bytes);
   void* p = nullptr;
   cudaError_t e = cudaMalloc(&p, total);
   if (e == cudaSuccess) e = cudaMemset(p, 0, total);
@@ -395,6 +521,20 @@ extern "C" int nvllm_ar_set_wait_ms(int64_t ms) {
   return NVLLM_OK;
 }
 
+extern "C" int nvllm_ar_set_protocol(int32_t protocol) {
+  ar::State* s = ar::current_state();
+  if (!s || !s->ready) return fail(NVLLM_E_GEOMETRY, "ar_set_protocol: nvllm_ar_init has not run on this device");
+  if (protocol < ar::kAuto || protocol > ar::kTwoShot) return fail(NVLLM_E_GEOMETRY, "ar_set_protocol: %d is not 0..3", protocol);
+  s->force = protocol;
+  return NVLLM_OK;
+}
+
+extern "C" int nvllm_ar_protocol(int64_t n_elems, int32_t world, int64_t max_bytes, int32_t forced) {
+  if (n_elems <= 0 || world < 2 || world > ar::kMaxRanks || max_bytes <= 0)
+    return fail(NVLLM_E_GEOMETRY, "ar_protocol: sizes invalid");
+  return ar::pick_protocol(n_elems / 8, n_elems % 8, max_bytes, world, forced);
+}
+
 extern "C" int64_t nvllm_ar_max_bytes(void) {
   ar::State* s = ar::current_state();
   return (s && s->connected) ? s->stage_bytes : 0;
@@ -419,6 +559,7 @@ extern "C" int nvllm_ar_allreduce(const void* in, void* out, int64_t n_elems, vo
   p.wait_cycles = s->wait_cycles;
   p.rank = s->rank;
   p.world = s->world;
+  p.force = s->force;
   p.peers = s->peers;
   p.status = status_word();
   if (!p.status) return fail(NVLLM_E_NO_DEVICE, "ar_allreduce: no CUDA device is usable");
@@ -428,13 +569,14 @@ extern "C" int nvllm_ar_allreduce(const void* in, void* out, int64_t n_elems, vo
 }
 
 extern "C" int64_t nvllm_ar_emulated_scratch_bytes(int32_t world, int64_t max_bytes) {
-  return static_cast<int64_t>(world) * (ar::kHeaderBytes + 4 * max_bytes);
+  return static_cast<int64_t>(world) * (ar::kHeaderBytes + ar::kAreas * max_bytes);
 }
 
 extern "C" int nvllm_ar_allreduce_emulated(int32_t world, const void* const* inputs, void* const* outputs, int64_t n_elems,
                                            void* scratch, int64_t scratch_bytes, int64_t max_bytes, int32_t absent_rank,
-                                           void* stream) {
+                                           int32_t protocol, void* stream) {
   if (world < 2 || world > ar::kMaxRanks) return fail(NVLLM_E_GEOMETRY, "ar_allreduce_emulated: world=%d invalid", world);
+  if (protocol < ar::kAuto || protocol > ar::kTwoShot) return fail(NVLLM_E_GEOMETRY, "ar_allreduce_emulated: protocol=%d invalid", protocol);
   if (!inputs || !outputs || !scratch) return fail(NVLLM_E_NULL, "ar_allreduce_emulated: NULL pointer argument");
   if (max_bytes <= 0 || max_bytes % 16 || n_elems <= 0 || (n_elems * 2 + 15) / 16 * 16 > max_bytes)
     return fail(NVLLM_E_GEOMETRY, "ar_allreduce_emulated: sizes invalid");
@@ -447,13 +589,14 @@ extern "C" int nvllm_ar_allreduce_emulated(int32_t world, const void* const* inp
   ep.base.wait_cycles = sm100::kWaitLimitCycles;
   ep.base.rank = 0;
   ep.base.world = world;
+  ep.base.force = protocol;
   ep.base.status = status_word();
   ep.base.in = nullptr;
   ep.base.out = nullptr;
   ep.absent_rank = absent_rank;
   if (!ep.base.status) return fail(NVLLM_E_NO_DEVICE, "ar_allreduce_emulated: no CUDA device is usable");
   for (int r = 0; r < ar::kMaxRanks; ++r) {
-    ep.base.peers.base[r] = r < world ? static_cast<unsigned char*>(scratch) + r * (ar::kHeaderBytes + 4 * max_bytes) : nullptr;
+    ep.base.peers.base[r] = r < world ? static_cast<unsigned char*>(scratch) + r * (ar::kHeaderBytes + ar::kAreas * max_bytes) : nullptr;
     ep.in[r] = r < world ? static_cast<const uint4*>(inputs[r]) : nullptr;
     ep.out[r] = r < world ? static_cast<uint4*>(outputs[r]) : nullptr;
     if (r < world && (!aligned16(inputs[r]) || !aligned16(outputs[r])))

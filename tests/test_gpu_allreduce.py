@@ -38,6 +38,36 @@ def test_emulated_ranks_sum_bit_exactly_call_after_call(cuda, world):
     assert _lib.read_status() == 0
 
 
+@pytest.mark.parametrize("world", [4, 8])
+def test_emulated_protocols_interleave(cuda, world):
+    """Cells, one shot and two shots in turn on one area (they share flags, call counts and
+    staging buffers), decode-step sizes; every rank must hold the oracle's sum bit for bit."""
+    scratch = _scratch(cuda, world)
+    g = torch.Generator().manual_seed(10 + world)
+    sizes = [256 * 1024, 16 * 1024, 64 * 4096, 256 * 4096, 8 * world, 1000 * 8, 256 * 1024]
+    for i, n in enumerate(sizes * 2):
+        proto = (3, 2, 1, 0)[i % 4]
+        xs = [(torch.randn(n, generator=g) * 2).to(torch.bfloat16) for _ in range(world)]
+        outs = AR.all_reduce_emulated([x.to(cuda) for x in xs], scratch, MAX_BYTES, protocol=proto)
+        torch.cuda.synchronize()
+        want = R.allreduce_ref(xs)
+        for r, o in enumerate(outs):
+            assert torch.equal(o.cpu().view(torch.int16), want.view(torch.int16)), f"call {i}, rank {r}, {n} elements"
+    assert _lib.read_status() == 0
+
+
+def test_absent_peer_in_the_two_shot_protocol(cuda):
+    """Rank 2 of 4 never arrives: both hand-shakes of the other ranks run out, nothing hangs."""
+    import time
+    scratch = _scratch(cuda, 4)
+    xs = [torch.ones(256 * 1024, dtype=torch.bfloat16, device=cuda) for _ in range(4)]
+    t0 = time.time()
+    AR.all_reduce_emulated(xs, scratch, MAX_BYTES, absent_rank=2, protocol=3)
+    torch.cuda.synchronize()
+    assert time.time() - t0 < 10
+    assert _lib.read_status() & 4, "NVLLM_STATUS_TIMEOUT expected"
+
+
 @pytest.mark.parametrize("n", [4096, 1024 * 1024 + 8])
 def test_absent_peer_times_out_without_hanging(cuda, n):
     """Rank 1 never arrives: the others give up after the clock limit, set the TIMEOUT bit and a

@@ -104,5 +104,20 @@ def test_when_the_peer_memory_all_reduce_is_preferred():
     assert prefer(256 * 1024 * 2, 2, mb) and prefer(256 * 4096 * 2, 2, mb) and prefer(4 << 20, 2, mb)
     assert not prefer(16384 * 1024 * 2, 2, mb)            # a 16k-token prefill batch: 32 MiB
     assert prefer(256 * 1024 * 2, 4, mb) and prefer(256 * 1024 * 2, 8, mb)
-    assert not prefer(256 * 4096 * 2, 4, mb) and not prefer(256 * 4096 * 2, 8, mb)
+    assert prefer(256 * 4096 * 2, 4, mb) and prefer(256 * 4096 * 2, 8, mb)
     assert not prefer(0, 2, mb)
+
+
+def test_all_reduce_protocol_choice_is_host_arithmetic(lib):
+    """Cells for small tensors, two shots for larger ones at more than two ranks, one shot at two
+    ranks and for tensors with a ragged tail; a forced protocol that does not apply falls back."""
+    from nano_vllm_b200.allreduce import protocol_for
+    mb = 8 << 20
+    assert protocol_for(32 << 10, 2, mb) == "cells" and protocol_for(2 << 20, 2, mb) == "cells"
+    assert protocol_for(4 << 20, 2, mb) == "one-shot"
+    assert protocol_for(32 << 10, 8, mb) == "cells"
+    assert protocol_for(512 << 10, 8, mb) == "two-shot" and protocol_for(2 << 20, 4, mb) == "two-shot"
+    assert protocol_for((2 << 20) + 6, 8, mb) == "one-shot"          # 3 elements beyond a whole vector
+    assert protocol_for(2 << 20, 8, mb, forced=2) == "one-shot"
+    assert protocol_for(2 << 20, 2, mb, forced=3) == "cells"           # two shots need more than two ranks
+    assert protocol_for(2 << 20, 8, mb, forced=1) == "two-shot"        # cells do not fit: 2 x 2 MiB x 8 > 8 MiB
