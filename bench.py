@@ -67,6 +67,9 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=256, help="sequences in the decode batch")
+    ap.add_argument("--shard-of", type=int, default=0, choices=[0, 2, 4, 8],
+                    help="with --gpus 1: time rank 0's shard of a run on that many GPUs (profiling aid: the per-rank "
+                         "launch of a tensor-parallel run on one GPU)")
     ap.add_argument("--repeats", type=int, default=0, help="timed regions of --steps steps (0: as many as give 0.5 s)")
     ap.add_argument("--no-secondary", action="store_true", help="skip the store/prefill/long-context extras")
     ap.add_argument("--no-engine", action="store_true",
@@ -298,7 +301,8 @@ def run_ours(args):
 
     build_once(local, barrier)
 
-    case = W.cfg4_decode(world, rank, dev, batch=args.batch)
+    shard_of = args.shard_of if world == 1 and args.shard_of else world
+    case = W.cfg4_decode(shard_of, rank, dev, batch=args.batch)
     B, Hq, Hkv, D = case.geometry
     lens_host = case.context_lens.cpu()
     decode_bytes_rank = W.decode_bytes(lens_host, Hq, Hkv, D)
@@ -417,7 +421,8 @@ def run_ours(args):
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "repeats": repeats, "ms_per_step_min_max": [round(min(region_ms) / args.steps, 4), round(max(region_ms) / args.steps, 4)],
         "ms_x_sm_mhz": round(ms_per_step * mhz, 1) if mhz else None,
-        "config": {"workload": workload_name(world), "global_batch": B, "kv_bytes_per_step": int(total_bytes),
+        "config": {"workload": workload_name(shard_of) + (f" -- rank 0's shard only, on one GPU" if shard_of != world else ""),
+                   "global_batch": B, "kv_bytes_per_step": int(total_bytes),
                    "decode_plan": {"unit_tokens": unit_tokens, "thread_blocks": ctas},
                    "l2": "inputs (KV cache shard) larger than L2, re-read every step; no flush needed",
                    "parallelism": f"tp{world}"},
@@ -436,7 +441,7 @@ def run_ours(args):
         "device_status_word": status,
     }
 
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and shard_of == 1:
         n_cpu = min(B, CPU_BASELINE_SEQS)
         sample_case = cpu_sample(case, n_cpu)
         gbs, dt, nbytes, threads = time_cpu_reference(sample_case, steps=10, warmup=1)
@@ -452,7 +457,7 @@ def run_ours(args):
         dist.barrier()
         dist.destroy_process_group()
     if rank == 0:
-        if not args.no_engine:
+        if not args.no_engine and shard_of == world:
             line["engine"] = engine_runs(world)
             mine = line["engine"].get("qwen3-0.6b", {}).get("b200", {})
             if "value" in mine:
