@@ -13,6 +13,11 @@
 // still in its last softmax, and the tensor pipe runs the next item's first S product under
 // the current item's epilogue.
 //
+// Order of the items: sequences longest first (ranked in shared memory by every block at start-up,
+// for batches of up to SORT_BATCH sequences), a sequence's long tiles first, head groups fastest.
+// The blocks that are still busy when the counter runs out are then working on the cheapest
+// items, so the launch ends without a tail of half-idle SMs.
+//
 // Item hand-off: the producer lane decodes an item into one of two descriptor slots in shared
 // memory (ITEM_FULL / ITEM_FREE barriers).  All rings keep running across items: tile t of the
 // block's life uses stage t&1 and barrier phase (t>>1)&1, so the next item's first K/V tiles
@@ -35,6 +40,7 @@ using namespace sm100;
 namespace tcp {
 using namespace tc;
 constexpr int MAX_BATCH = 1024;  // prefix array of query tiles per sequence lives in shared memory
+constexpr int SORT_BATCH = 256;  // batches up to this size are ranked by length (B^2 / 192 compares per thread)
 enum PBar {
   ITEM_FULL0 = tc::NUM_BARS, ITEM_FULL1, ITEM_FREE0, ITEM_FREE1, O_FREE, P_NUM_BARS
 };
@@ -52,7 +58,8 @@ struct Geo {
   static constexpr int OFF_SLOTS = OFF_CTRL + 256;         // two item descriptors of 8 ints
   static constexpr int OFF_MISC = OFF_SLOTS + 64;          // tmem address, abort flag
   static constexpr int OFF_PREFIX = OFF_MISC + 64;         // (MAX_BATCH + 1) ints
-  static constexpr int SMEM = OFF_PREFIX + (MAX_BATCH + 1) * 4 + 60 + 1024;
+  static constexpr int OFF_ORDER = OFF_PREFIX + (MAX_BATCH + 1) * 4 + 60;  // MAX_BATCH u16: sequences, longest first
+  static constexpr int SMEM = OFF_ORDER + MAX_BATCH * 2 + 1024;
   static constexpr int OCH = D / 32;      // 32-column chunks of O
   static constexpr int ROWB = D * 2;      // bytes of one output row
   static constexpr int PIECES = D / 8;    // 16-byte pieces of one row
@@ -64,6 +71,19 @@ static_assert(P_NUM_BARS * 8 <= 256, "barrier area");
 // Work counters, one pair per launch slot; the last block of a launch to leave resets its pair.
 __device__ unsigned int g_item_counter[tcp::NUM_SLOTS];
 __device__ unsigned int g_done_counter[tcp::NUM_SLOTS];
+
+#ifdef NVLLM_PREFILL_PROFILE
+// Development build only: where the first softmax warp of every block spends its cycles
+// (8 counters per block), read back through nvllm_debug_prefill_profile.
+__device__ unsigned long long g_prefill_prof[2048 * 8];
+#define PROF_DECL long long prof_t = clock64(); unsigned long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define PROF(i) do { const long long now_ = clock64(); prof[i] += now_ - prof_t; prof_t = now_; } while (0)
+#define PROF_COUNT(i) (++prof[i])
+#else
+#define PROF_DECL
+#define PROF(i)
+#define PROF_COUNT(i)
+#endif
 
 struct Item {
   int b, h, m0, q0, Lq, k0, Lk, n_kv;  // n_kv < 0: no more work
@@ -78,7 +98,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
   using G = Geo<D>;
   constexpr int Q_SUB = G::Q_SUB, KV_BYTES = G::KV_BYTES, KV_SUB = G::KV_SUB;
   constexpr int OFF_Q = G::OFF_Q, OFF_K = G::OFF_K, OFF_V = G::OFF_V, OFF_CTRL = G::OFF_CTRL;
-  constexpr int OFF_SLOTS = G::OFF_SLOTS, OFF_MISC = G::OFF_MISC, OFF_PREFIX = G::OFF_PREFIX;
+  constexpr int OFF_SLOTS = G::OFF_SLOTS, OFF_MISC = G::OFF_MISC, OFF_PREFIX = G::OFF_PREFIX, OFF_ORDER = G::OFF_ORDER;
   constexpr int OCH = G::OCH, PIECES = G::PIECES;
   extern __shared__ unsigned char smem_raw[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -90,27 +110,59 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
   volatile int* slots = reinterpret_cast<volatile int*>(base_ptr + OFF_SLOTS);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + OFF_MISC + 8);
-  int* prefix = reinterpret_cast<int*>(base_ptr + OFF_PREFIX);  // prefix[b] = query tiles before sequence b
+  int* prefix = reinterpret_cast<int*>(base_ptr + OFF_PREFIX);  // prefix[i] = query tiles before the i-th sequence in order
+  unsigned short* order = reinterpret_cast<unsigned short*>(base_ptr + OFF_ORDER);  // order[i] = i-th longest sequence
   // Head packing: the rows of a tile are BMT = 128 / n query tokens x n query heads of one KV head
   // (row = token * n + head; n = p.pack need not be a power of two: 7 heads x 18 tokens leave two
   // rows unused), so short and ragged sequences waste fewer rows above the diagonal and past
   // their end, and the packed heads share every K/V tile.
   const int pack = p.pack, BMT = BM / pack;
 
+  // Rank the sequences by key length, longest first (ties by index): rank = how many come before.
+  if (p.batch <= SORT_BATCH) {
+    for (int b = tid; b < p.batch; b += NTHREADS) prefix[b] = p.cu_k[b + 1] - p.cu_k[b];  // lengths, for a moment
+    __syncthreads();
+    int my_rank[(SORT_BATCH + NTHREADS - 1) / NTHREADS];
+#pragma unroll
+    for (int k = 0; k < (SORT_BATCH + NTHREADS - 1) / NTHREADS; ++k) {
+      const int b = tid + k * NTHREADS;
+      int rank = 0;
+      if (b < p.batch) {
+        const int mine = prefix[b];
+        for (int o = 0; o < p.batch; ++o) {
+          const int theirs = prefix[o];
+          rank += (theirs > mine) || (theirs == mine && o < b);
+        }
+      }
+      my_rank[k] = rank;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < (SORT_BATCH + NTHREADS - 1) / NTHREADS; ++k) {
+      const int b = tid + k * NTHREADS;
+      if (b < p.batch) order[my_rank[k]] = static_cast<unsigned short>(b);
+    }
+  } else {
+    for (int b = tid; b < p.batch; b += NTHREADS) order[b] = static_cast<unsigned short>(b);
+  }
+  __syncthreads();
   if (warp == 4) {
-    // query tiles per sequence -> exclusive prefix sum (warp scan, 32 sequences at a time)
+    // query tiles per sequence, in that order -> exclusive prefix sum (warp scan, 32 at a time)
     int carry = 0;
-    for (int b0 = 0; b0 < p.batch; b0 += 32) {
-      const int b = b0 + lane;
+    for (int i0 = 0; i0 < p.batch; i0 += 32) {
+      const int i = i0 + lane;
       int tiles = 0;
-      if (b < p.batch) tiles = (p.cu_q[b + 1] - p.cu_q[b] + BMT - 1) / BMT;
+      if (i < p.batch) {
+        const int b = order[i];
+        tiles = (p.cu_q[b + 1] - p.cu_q[b] + BMT - 1) / BMT;
+      }
       int incl = tiles;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
         const int v = __shfl_up_sync(0xffffffffu, incl, d);
         if (lane >= d) incl += v;
       }
-      if (b < p.batch) prefix[b] = carry + incl - tiles;
+      if (i < p.batch) prefix[i] = carry + incl - tiles;
       carry += __shfl_sync(0xffffffffu, incl, 31);
     }
     if (lane == 0) {
@@ -160,16 +212,16 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
           if (idx >= static_cast<unsigned>(total_items)) break;
           const int pi = idx / hgroups;
           x.h = (idx - pi * hgroups) * pack;  // first of the packed heads
-          int lo = 0, hi = p.batch;  // largest b with prefix[b] <= pi
+          int lo = 0, hi = p.batch;  // largest i with prefix[i] <= pi
           while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
             if (prefix[mid] <= pi) lo = mid; else hi = mid;
           }
-          x.b = lo;
-          x.q0 = p.cu_q[lo];
-          x.Lq = p.cu_q[lo + 1] - x.q0;
-          x.k0 = p.cu_k[lo];
-          x.Lk = p.cu_k[lo + 1] - x.k0;
+          x.b = order[lo];
+          x.q0 = p.cu_q[x.b];
+          x.Lq = p.cu_q[x.b + 1] - x.q0;
+          x.k0 = p.cu_k[x.b];
+          x.Lk = p.cu_k[x.b + 1] - x.k0;
           const int tiles = prefix[lo + 1] - prefix[lo];
           x.m0 = (tiles - 1 - (pi - prefix[lo])) * BMT;  // a sequence's long tiles first
           const int kv_end = min(x.Lk, min(x.m0 + BMT, x.Lq) + (x.Lk - x.Lq));
@@ -291,16 +343,21 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
     unsigned char* stage = base_ptr + G::OFF_STAGE + warp * 2048;  // this warp's 32 rows x 64 B
     int T = 0;
     bool ok = true;
+    PROF_DECL;
     for (int it = 0; ok; ++it) {
       if (!(ok = wait_or_abort(bar(ITEM_FULL0 + (it & 1)), (it >> 1) & 1, abort_flag))) break;
       const Item x = read_item(it);
+      PROF(0);  // waiting for the next item
       if (x.n_kv < 0) break;
+      PROF_COUNT(6);
       const int qi = x.m0 + r_tok, off = x.Lk - x.Lq;
       float m_used = -INFINITY, l = 0.f;
       for (int j = 0; j < x.n_kv; ++j) {
         const int t = T + j, st = t & 1, ph = (t >> 1) & 1;
         const uint32_t tmem_s = tmem + st * 64 + lane_addr;
         if (!(ok = wait_or_abort(bar(QK_DONE0 + st), ph, abort_flag))) break;
+        PROF(1);  // waiting for the scores
+        PROF_COUNT(7);
         tc_fence_after();
         uint32_t s[64];
         tmem_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
@@ -334,7 +391,9 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
             l *= alpha;
           }
           if (j > 0) {  // O holds tiles 0..j-1 of this item once the previous P V product has finished
+            PROF(2);
             if (!(ok = wait_or_abort(bar(PV_DONE0 + ((t - 1) & 1)), ((t - 1) >> 1) & 1, abort_flag))) break;
+            PROF(3);  // waiting for O before a rescale
             tc_fence_after();
 #pragma unroll
             for (int c = 0; c < OCH; ++c) {
@@ -383,12 +442,14 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(P_FULL0 + st));
+        PROF(2);  // softmax of one tile
       }
       if (!ok) break;
       T += x.n_kv;
 
       // epilogue: O / l -> bf16; 32 columns at a time through this warp's patch of shared memory
       if (!(ok = wait_or_abort(bar(PV_DONE0 + ((T - 1) & 1)), ((T - 1) >> 1) & 1, abort_flag))) break;
+      PROF(4);  // waiting for the last product before the epilogue
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
       // lane -> (row, 16-byte piece) of the eight 64-byte row segments one store instruction writes
@@ -429,7 +490,12 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
         __syncwarp();
       }
       if (lane == 0) mbar_arrive(bar(ITEM_FREE0 + (it & 1)));
+      PROF(5);  // epilogue
     }
+#ifdef NVLLM_PREFILL_PROFILE
+    if (tid == 0 && blockIdx.x < 2048)
+      for (int i = 0; i < 8; ++i) g_prefill_prof[blockIdx.x * 8 + i] = prof[i];
+#endif
   }
 
   tc_fence_before();
@@ -495,6 +561,13 @@ static int launch_prefill_tcp_t(const PrefillParams& p_in, int64_t total_q, int6
   count_launch();
   return check_launch("prefill (tcgen05, persistent) launch");
 }
+
+#ifdef NVLLM_PREFILL_PROFILE
+extern "C" NVLLM_API int nvllm_debug_prefill_profile(unsigned long long* host_out, int n_blocks) {
+  if (n_blocks > 2048) n_blocks = 2048;
+  return cudaMemcpyFromSymbol(host_out, g_prefill_prof, sizeof(unsigned long long) * 8 * n_blocks) == cudaSuccess ? 0 : -5;
+}
+#endif
 
 int launch_prefill_tcp(const PrefillParams& p, int64_t total_q, int64_t total_k, cudaStream_t stream) {
   if (p.d == 128) return launch_prefill_tcp_t<128>(p, total_q, total_k, stream);
