@@ -61,7 +61,6 @@ extern "C" {
 #define NVLLM_STATUS_BAD_SLOT 1  /* store_kvcache saw slot >= num_slots (row skipped) */
 #define NVLLM_STATUS_BAD_BLOCK 2 /* a block_tables entry in use was outside [0,num_blocks) */
 #define NVLLM_STATUS_TIMEOUT 4   /* a bounded in-kernel wait expired; that launch's output is invalid */
-#define NVLLM_STATUS_INTERNAL 8  /* a kernel found its own layout assumption broken (shared-memory alignment) */
 
 /*
  * Scatter the new tokens' K and V rows into the paged cache.

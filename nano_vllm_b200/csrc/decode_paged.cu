@@ -16,14 +16,9 @@
 //     context_lens itself (a block-wide scan of the units per sequence), so blocks carry the
 //     same number of bytes whatever the lengths are: no tail of half-empty waves, one ramp-up.
 //   * A thread block has NW warps that do not synchronise with one another while streaming.
-//     Warp w owns the TT-token tile w of every unit and runs its own NST-stage ring fed by TMA:
-//     one lane issues a tiled bulk copy per 64-element half of the K tile and of the V tile
-//     (cp.async.bulk.tensor, 128-byte swizzle so ldmatrix is conflict free, no multicast) and
-//     the warp waits on the stage's mbarrier.  A tile costs a handful of instructions instead of
-//     one address computation per 16 bytes, which leaves the issue slots (and the power) to the
-//     arithmetic.  The ring keeps running across sequence boundaries.  Rows past the end of a
-//     context are masked out of the scores and their V rows cleared in shared memory, so stale
-//     cache contents never reach the output.
+//     Warp w owns the TT-token tile w of every unit and runs its own NST-stage cp.async ring
+//     (16-byte copies, XOR-swizzled rows so ldmatrix is conflict free).  The ring keeps running
+//     across sequence boundaries.  Rows past the end of a context are zero-filled, never read.
 //   * Tensor cores do the dot products with the tokens on the M side so that G <= 8 query
 //     heads fit the N=8 side without padding M: S^T[16 tok x 8 heads] = K[16 x D] Q^T[D x 8]
 //     and O^T[D x 8] += V^T[D x 16] P^T[16 x 8] (mma.sync.m16n8k16, bf16 in / fp32 out).
@@ -39,7 +34,6 @@
 #include <cstdlib>
 
 #include "common.cuh"
-#include "sm100.cuh"
 
 // Pipeline shape of the head_dim-128 kernel: tokens per warp tile, ring stages per warp, warps per
 // block (overridable at build time for sweeps; the defaults are the measured best).
@@ -95,17 +89,12 @@ struct DecodeCfg {
   static constexpr int UNIT = NW * TT;               // tokens per work unit
   static constexpr int CPR = D / 8;                  // 16-byte pieces per row
   static constexpr int ROW_BYTES = D * 2;
-  static constexpr int NHALF = D / 64;               // 64-element (128-byte) halves of a row
-  static constexpr int HALF_BYTES = TT * 128;        // one half of one tile: TT rows of 128 bytes
-  static constexpr int TILE_BYTES = TT * ROW_BYTES;  // one tensor, one stage: [half][row][128 B]
+  static constexpr int TILE_BYTES = TT * ROW_BYTES;  // one tensor, one stage
   static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
   static constexpr int WARP_BYTES = NST * STAGE_BYTES;
   static constexpr int RING_BYTES = NW * WARP_BYTES;
   static constexpr int MERGE_BYTES = NW * 8 * D * 4 + NW * 8 * 2 * 4;
-  static constexpr int OFF_BARS = RING_BYTES + MERGE_BYTES;  // NW * NST mbarriers
-  static constexpr int OFF_MISC = OFF_BARS + NW * NST * 8;   // scan scratch, range start, arrival flag
-  static constexpr int SMEM = OFF_MISC + 64;
-  static_assert(HALF_BYTES % 1024 == 0, "a half tile must be whole 1024-byte swizzle atoms");
+  static constexpr int SMEM = RING_BYTES + MERGE_BYTES;
   static constexpr int MT = TT / 16;  // 16-token MMA row tiles per warp tile
   static constexpr int KS = D / 16;   // k-steps of the QK^T product
   static constexpr int DT = D / 16;   // 16-row tiles of O^T
@@ -119,28 +108,16 @@ struct SeqCursor {
 };
 
 template <class C>
-__global__ void __launch_bounds__(C::NW * 32, 2)
-decode_paged_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v) {
-  using namespace sm100;
+__global__ void __launch_bounds__(C::NW * 32, 2) decode_paged_kernel(const DecodeParams p) {
   constexpr int D = C::D, TT = C::TT, NST = C::NST, NW = C::NW, UNIT = C::UNIT, NT = NW * 32;
-  // No static shared memory: the dynamic area then starts on a 1024-byte boundary, which the
-  // 128-byte swizzle of the tiles assumes (checked below).
-  extern __shared__ __align__(1024) unsigned char smem[];
-  int* s_scan = reinterpret_cast<int*>(smem + C::OFF_MISC);  // [NW]
-  int* s_start = s_scan + NW;                                // [2]
-  int* s_last_arrival = s_start + 2;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ int s_scan[NW];
+  __shared__ int s_start[2];
+  __shared__ int s_last_arrival;
 
   pdl_prologue();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int gid = lane >> 2, tig = lane & 3;
-  const uint32_t bars = smem_u32(smem) + C::OFF_BARS;
-  if (tid == 0) {
-    if (smem_u32(smem) & 1023u) atomicOr(p.status, NVLLM_STATUS_INTERNAL);
-    for (int i = 0; i < NW * NST; ++i) mbar_init(bars + 8u * i, 1);
-    mbar_fence_init();
-    prefetch_tmap(&tmap_k);
-    prefetch_tmap(&tmap_v);
-  }
   const int kvh = blockIdx.x % p.hkv;
   const int range = blockIdx.x / p.hkv;
   const int ctx_cap = p.max_blocks * kBlockSize;
@@ -238,33 +215,47 @@ decode_paged_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
   const uint32_t warp_smem = smem_u32(smem) + warp * C::WARP_BYTES;
   const int64_t row_elems = static_cast<int64_t>(p.hkv) * D;
 
-  // Chunk `col` (16 bytes) of row r of a tile: [half][row][128 B], chunks XOR-swizzled by the row.
-  auto chunk_off = [](int r, int col) { return (col >> 3) * C::HALF_BYTES + r * 128 + (((col & 7) ^ (r & 7)) << 4); };
-  const uint32_t warp_bars = bars + 8u * (warp * NST);
-
-  // Slot `slot` of this warp's ring <- the warp's tile of unit u (sequence c).  One lane issues
-  // the copies; a warp without tokens in a sequence's last unit still completes the phase.
-  auto load_tile = [&](const SeqCursor& c, int u, int slot) {
-    if (lane != 0) return;
-    const int stage = slot % NST;
-    const uint32_t bar = warp_bars + 8u * stage;
+  auto load_tile = [&](const SeqCursor& c, int u, int stage) {
     const int t0 = (u - c.first) * UNIT + warp * TT;
-    if (t0 >= c.ctx) {
-      mbar_arrive(bar);
-      return;
-    }
+    if (t0 >= c.ctx) return;  // this warp has no token in the sequence's last unit
     int64_t blk = p.block_tables[c.b * p.bt_stride + t0 / kBlockSize];
-    if (blk < 0 || blk >= p.num_blocks) {
-      atomicOr(p.status, NVLLM_STATUS_BAD_BLOCK);
+    const bool blk_ok = blk >= 0 && blk < p.num_blocks;
+    if (!blk_ok) {
+      if (lane == 0) atomicOr(p.status, NVLLM_STATUS_BAD_BLOCK);
       blk = 0;
     }
-    const int row = static_cast<int>(blk * kBlockSize + (t0 % kBlockSize));
+    const int64_t slot0 = blk * kBlockSize + (t0 % kBlockSize);
+    // Step variant: token ctx-1 is the one being decoded.  Its row comes from the activation
+    // and goes to the cache from here, provided slot_mapping agrees with the block table.
+    const int last = c.ctx - 1;
+    bool take_new = false;
+    if (p.k_new != nullptr && last < t0 + TT) {  // last >= t0 holds because t0 < ctx
+      const int32_t slot = p.slot_mapping[c.b];
+      if (slot >= 0) {
+        if (blk_ok && slot == slot0 + (last - t0)) take_new = true;
+        else if (lane == 0) atomicOr(p.status, NVLLM_STATUS_BAD_SLOT);
+      }
+    }
     const uint32_t kdst = warp_smem + stage * C::STAGE_BYTES;
-    mbar_expect_tx(bar, C::STAGE_BYTES);
 #pragma unroll
-    for (int h = 0; h < C::NHALF; ++h) {
-      tma_load_3d(kdst + h * C::HALF_BYTES, &tmap_k, bar, h * 64, kvh, row);
-      tma_load_3d(kdst + C::TILE_BYTES + h * C::HALF_BYTES, &tmap_v, bar, h * 64, kvh, row);
+    for (int it = 0; it < TT * C::CPR / 32; ++it) {
+      const int idx = it * 32 + lane;
+      const int r = idx / C::CPR, col = idx % C::CPR;
+      const int bytes = (blk_ok && t0 + r < c.ctx) ? 16 : 0;
+      const int64_t off = bytes ? (slot0 + r) * row_elems + kvh * D + col * 8 : 0;
+      const uint32_t dst = kdst + r * C::ROW_BYTES + ((col ^ (r & 7)) << 4);
+      if (take_new && t0 + r == last) {
+        const int64_t in_row = static_cast<int64_t>(kvh) * D + col * 8;
+        const uint4 kk = *reinterpret_cast<const uint4*>(p.k_new + c.b * p.k_new_stride + in_row);
+        const uint4 vv = *reinterpret_cast<const uint4*>(p.v_new + c.b * p.v_new_stride + in_row);
+        *reinterpret_cast<uint4*>(p.k_cache + off) = kk;
+        *reinterpret_cast<uint4*>(p.v_cache + off) = vv;
+        st_shared16(dst, kk);
+        st_shared16(dst + C::TILE_BYTES, vv);
+      } else {
+        cp_async16(dst, p.k_cache + off, bytes);
+        cp_async16(dst + C::TILE_BYTES, p.v_cache + off, bytes);
+      }
     }
   };
 
@@ -338,10 +329,10 @@ decode_paged_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
       __syncthreads();
       if (tid == 0) {
         const unsigned int arrived = atomicAdd(&p.counters[cc.b * p.hkv + kvh], 1u);
-        *s_last_arrival = arrived == static_cast<unsigned int>(n_parts - 1);
+        s_last_arrival = arrived == static_cast<unsigned int>(n_parts - 1);
       }
       __syncthreads();
-      if (*s_last_arrival) {  // every piece is in the workspace: merge them in range order
+      if (s_last_arrival) {  // every piece is in the workspace: merge them in range order
         __threadfence();
         for (int idx = tid; idx < p.g * D; idx += NT) {
           const int h = idx / D, d = idx % D;
@@ -372,6 +363,7 @@ decode_paged_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
       seek(pc, u0 + j);
       load_tile(pc, u0 + j, j);
     }
+    cp_async_commit();
   }
 
   for (int i = 0;; ++i) {
@@ -393,53 +385,19 @@ decode_paged_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
       qn_b = min(cc.b + 1, p.batch - 1);
       load_q(qn, qn_b);
     }
-    __syncwarp();  // every lane is done with slot i-1, whose stage the next copy overwrites
+    cp_async_wait<NST - 2>();
+    __syncwarp();
     if (i + NST - 1 < n_units) {
       seek(pc, u + NST - 1);
-      load_tile(pc, u + NST - 1, i + NST - 1);
+      load_tile(pc, u + NST - 1, (i + NST - 1) % NST);
     }
+    cp_async_commit();
 
     const int t0 = (u - cc.first) * UNIT + warp * TT;
     if (t0 >= cc.ctx) continue;
     const int t_end = cc.ctx;
     const uint32_t kbase = warp_smem + (i % NST) * C::STAGE_BYTES;
     const uint32_t vbase = kbase + C::TILE_BYTES;
-    if (!mbar_wait(warp_bars + 8u * (i % NST), (i / NST) & 1) && lane == 0) atomicOr(p.status, NVLLM_STATUS_TIMEOUT);
-
-    if (t0 + TT > t_end || p.k_new != nullptr) {  // the sequence's last tile (warp-uniform)
-      const int last = t_end - 1;
-      if (last < t0 + TT) {
-        // rows past the context hold whatever the cache block has there: their scores are masked
-        // below, and their V rows are cleared so that 0 x NaN cannot reach the output
-        const int first_dead = t_end - t0;
-        for (int idx = first_dead * C::CPR + lane; idx < TT * C::CPR; idx += 32)
-          st_shared16(vbase + chunk_off(idx / C::CPR, idx % C::CPR), make_uint4(0u, 0u, 0u, 0u));
-        // Step variant: token ctx-1 is the one being decoded.  Its row comes from the activation
-        // and goes to the cache from here, provided slot_mapping agrees with the block table.
-        if (p.k_new != nullptr) {
-          const int32_t slot = p.slot_mapping[cc.b];
-          const int64_t blk = p.block_tables[cc.b * p.bt_stride + last / kBlockSize];
-          if (slot >= 0) {
-            if (blk >= 0 && blk < p.num_blocks && slot == blk * kBlockSize + last % kBlockSize) {
-              if (lane < 2 * C::CPR) {
-                const int col = lane % C::CPR;
-                const bool is_v = lane >= C::CPR;
-                const int64_t in_off = static_cast<int64_t>(kvh) * D + col * 8;
-                const uint4 row16 = is_v ? *reinterpret_cast<const uint4*>(p.v_new + cc.b * p.v_new_stride + in_off)
-                                         : *reinterpret_cast<const uint4*>(p.k_new + cc.b * p.k_new_stride + in_off);
-                const int64_t off = static_cast<int64_t>(slot) * row_elems + in_off;
-                *reinterpret_cast<uint4*>((is_v ? p.v_cache : p.k_cache) + off) = row16;
-                st_shared16((is_v ? vbase : kbase) + chunk_off(last - t0, col), row16);
-              }
-            } else if (lane == 0) {
-              atomicOr(p.status, NVLLM_STATUS_BAD_SLOT);
-            }
-          }
-        }
-        fence_proxy_async();  // these plain stores are ordered before the bulk copy that reuses the stage
-        __syncwarp();
-      }
-    }
 
     // S^T = K Q^T
     float s[C::MT][4];
@@ -451,7 +409,7 @@ decode_paged_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
       for (int ks = 0; ks < C::KS; ++ks) {
         const int c = ks * 2 + (lane >> 4);
         uint32_t a0, a1, a2, a3;
-        ldmatrix_x4(a0, a1, a2, a3, kbase + chunk_off(r, c));
+        ldmatrix_x4(a0, a1, a2, a3, kbase + r * C::ROW_BYTES + ((c ^ (r & 7)) << 4));
         mma_bf16_16816(s[mt], a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
       }
     }
@@ -510,11 +468,12 @@ decode_paged_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap tm
       for (int dt = 0; dt < C::DT; ++dt) {
         const int c = dt * 2 + ((lane >> 3) & 1);
         uint32_t a0, a1, a2, a3;
-        ldmatrix_x4_trans(a0, a1, a2, a3, vbase + chunk_off(r, c));
+        ldmatrix_x4_trans(a0, a1, a2, a3, vbase + r * C::ROW_BYTES + ((c ^ (r & 7)) << 4));
         mma_bf16_16816(o[dt], a0, a1, a2, a3, pb0, pb1);
       }
     }
   }
+  cp_async_wait<0>();
 }
 
 // ---- host side -------------------------------------------------------------------------
@@ -563,36 +522,6 @@ static int64_t workspace_bytes_for(int batch, int hq, int hkv, int d) {
   return kCounterBytes + rows * d * 4 + rows * 2 * 4;
 }
 
-// Tensor maps of the cache planes, {head_dim, Hkv, slots} with a {64, 1, TT} box.  Encoding one
-// takes the driver about a microsecond; the planes of an engine are few and keep their
-// addresses, so the last ones are kept (direct-mapped by address).
-struct CachedMap {
-  const void* base = nullptr;
-  int hkv = 0, d = 0, box_rows = 0, dev = -1;
-  int64_t slots = 0;
-  CUtensorMap map;
-};
-static bool cache_plane_map(CUtensorMap* out, const void* base, int hkv, int d, int64_t slots, int box_rows) {
-  static CachedMap cache[256];
-  int dev = 0;
-  cudaGetDevice(&dev);
-  CachedMap& e = cache[(reinterpret_cast<uintptr_t>(base) >> 10) % 256];
-  if (e.base != base || e.hkv != hkv || e.d != d || e.slots != slots || e.box_rows != box_rows || e.dev != dev) {
-    if (!sm100::make_tmap_3d(&e.map, base, d, hkv, slots, d, static_cast<uint64_t>(hkv) * d, box_rows)) {
-      e.base = nullptr;
-      return false;
-    }
-    e.base = base;
-    e.hkv = hkv;
-    e.d = d;
-    e.slots = slots;
-    e.box_rows = box_rows;
-    e.dev = dev;
-  }
-  *out = e.map;
-  return true;
-}
-
 template <class C>
 static int launch_decode(const DecodeParams& p, cudaStream_t stream) {
   static bool attr_set[64] = {false};
@@ -603,13 +532,9 @@ static int launch_decode(const DecodeParams& p, cudaStream_t stream) {
     if (e != cudaSuccess) return fail(NVLLM_E_CUDA, "decode_paged: cannot reserve %d bytes of shared memory: %s", C::SMEM, cudaGetErrorString(e));
     attr_set[dev] = true;
   }
-  CUtensorMap mk, mv;
-  const int64_t slots = p.num_blocks * kBlockSize;
-  if (!cache_plane_map(&mk, p.k_cache, p.hkv, C::D, slots, C::TT) || !cache_plane_map(&mv, p.v_cache, p.hkv, C::D, slots, C::TT))
-    return NVLLM_E_CUDA;
   const int grid = p.n_ranges * p.hkv;
   cudaError_t e = launch_kernel(decode_paged_kernel<C>, dim3(static_cast<unsigned>(grid)), dim3(C::NW * 32), C::SMEM, stream,
-                                pdl_enabled(), p, mk, mv);
+                                pdl_enabled(), p);
   count_launch();
   if (e != cudaSuccess) {
     (void)cudaGetLastError();
