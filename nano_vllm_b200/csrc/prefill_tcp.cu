@@ -202,13 +202,12 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
       const int total_items = prefix[p.batch] * hgroups;
       int T = 0;   // key tiles loaded so far in this block's life
       int nq = 0;  // items with at least one key tile so far (Q_FULL phase)
-      for (int it = 0;; ++it) {
-        // next item: (query tile of a sequence, head); heads vary fastest so that the blocks
-        // working side by side share K/V tiles in L2
+      // Item number -> item: (query tile of a sequence, head); heads vary fastest so that the blocks
+      // working side by side share K/V tiles in L2.
+      auto decode_item = [&](unsigned idx) {
         Item x;
         while (true) {
           x.n_kv = -1;
-          const unsigned idx = atomicAdd(&g_item_counter[counter_slot], 1u);
           if (idx >= static_cast<unsigned>(total_items)) break;
           const int pi = idx / hgroups;
           x.h = (idx - pi * hgroups) * pack;  // first of the packed heads
@@ -233,13 +232,22 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
             uint4* dst = reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(x.q0 + r) * p.out_stride + x.h * D);
             for (int c = 0; c < PIECES * pack; ++c) dst[c] = make_uint4(0, 0, 0, 0);  // the packed heads are adjacent
           }
+          idx = atomicAdd(&g_item_counter[counter_slot], 1u);
         }
+        return x;
+      };
+      // The counter is read one item ahead: the round trip of the atomic runs under the loads
+      // and products of the current item instead of in front of the next one.
+      unsigned next_idx = atomicAdd(&g_item_counter[counter_slot], 1u);
+      for (int it = 0;; ++it) {
+        const Item x = decode_item(next_idx);
         if (it >= 2 && !wait_or_abort(bar(ITEM_FREE0 + (it & 1)), ((it >> 1) - 1) & 1, abort_flag)) break;
         volatile int* s = slots + (it & 1) * 8;
         s[0] = x.b; s[1] = x.h; s[2] = x.m0; s[3] = x.q0;
         s[4] = x.Lq; s[5] = x.k0; s[6] = x.Lk; s[7] = x.n_kv;
         mbar_arrive(bar(ITEM_FULL0 + (it & 1)));
         if (x.n_kv < 0) break;
+        next_idx = atomicAdd(&g_item_counter[counter_slot], 1u);
 
         const int kvh = x.h / p.g;
         // Q buffer: free once the last S product of the previous item is complete
@@ -341,6 +349,55 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
     const int r_tok = r / pack;  // this row's token within the tile (== BMT for the unused rows of a 7-head tile)
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     unsigned char* stage = base_ptr + G::OFF_STAGE + warp * 2048;  // this warp's 32 rows x 64 B
+    // Output side of the epilogue: one store instruction writes eight 64-byte row segments;
+    // lane -> (row, 16-byte piece).  The four rows a lane stores never change: token and head of
+    // each, and its offset in the output, are worked out once.
+    const int srow = lane >> 2, spiece = lane & 3;
+    int st_tok[4], st_off[4];  // a tile spans at most 128 output rows: the offsets fit 32 bits
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int row = warp * 32 + i * 8 + srow;  // row of the tile
+      st_tok[i] = row / pack;
+      st_off[i] = st_tok[i] * static_cast<int>(p.out_stride) + (row - st_tok[i] * pack) * D + spiece * 8;
+    }
+    // The epilogue of an item (O / l -> bf16 rows in the output) does not run when the item's last
+    // product is done: it is carried into the first key tile of the NEXT item and done there 32
+    // columns at a time between the stages of that tile's softmax, so that the TMEM loads, the
+    // pass through shared memory and the global stores fill the softmax's latency gaps instead of
+    // standing in front of it.  O is free for the next item's first product well before that
+    // tile's P is ready.  Only the block's last item has its epilogue on its own.
+    bool pend = false;
+    float pend_inv = 0.f;
+    __nv_bfloat16* pend_out = nullptr;
+    int pend_toks = 0, pend_t = 0;
+    // 32 columns of O (already in `o`) -> output rows; then starts the load of the next 32, or,
+    // after the last, releases O.
+    auto epilogue_chunk = [&](int c, uint32_t (&o)[32]) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        uint4 v;
+        v.x = pack_bf16x2(__uint_as_float(o[8 * k]) * pend_inv, __uint_as_float(o[8 * k + 1]) * pend_inv);
+        v.y = pack_bf16x2(__uint_as_float(o[8 * k + 2]) * pend_inv, __uint_as_float(o[8 * k + 3]) * pend_inv);
+        v.z = pack_bf16x2(__uint_as_float(o[8 * k + 4]) * pend_inv, __uint_as_float(o[8 * k + 5]) * pend_inv);
+        v.w = pack_bf16x2(__uint_as_float(o[8 * k + 6]) * pend_inv, __uint_as_float(o[8 * k + 7]) * pend_inv);
+        *reinterpret_cast<uint4*>(stage + lane * 64 + ((k ^ ((lane >> 1) & 3)) << 4)) = v;
+      }
+      if (c + 1 < OCH) {
+        tmem_ld32(tmem_o + lane_addr + (c + 1) * 32, o);
+      } else {  // O has been read: the next item's first product may overwrite it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(O_FREE));
+      }
+      __syncwarp();
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int lr = i * 8 + srow;  // row within the warp's 32
+        const uint4 v = *reinterpret_cast<const uint4*>(stage + lr * 64 + ((spiece ^ ((lr >> 1) & 3)) << 4));
+        if (st_tok[i] < pend_toks) *reinterpret_cast<uint4*>(pend_out + st_off[i] + c * 32) = v;
+      }
+      __syncwarp();
+    };
     int T = 0;
     bool ok = true;
     PROF_DECL;
@@ -362,7 +419,16 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
         uint32_t s[64];
         tmem_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
         tmem_ld32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+        const bool epi = pend && j == 0;  // warp-uniform: the previous item's epilogue rides on this tile
+        uint32_t ob[32];
+        if (epi) {
+          if (!(ok = wait_or_abort(bar(PV_DONE0 + (pend_t & 1)), (pend_t >> 1) & 1, abort_flag))) break;
+          PROF(4);  // waiting for the previous item's last product
+          tc_fence_after();
+          tmem_ld32(tmem_o + lane_addr, ob);
+        }
         tmem_wait_ld();
+        if (epi) epilogue_chunk(0, ob);
 
         const int j0 = j * BN;
         if ((j0 + BN - 1 > x.m0 + off) || (j0 + BN > x.Lk)) {  // tile touches the diagonal or the end
@@ -406,17 +472,41 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
             }
           }
         }
+        if (epi && OCH > 1) {
+          tmem_wait_ld();
+          epilogue_chunk(1, ob);
+        }
         const float msub = (m_used == -INFINITY) ? 0.f : m_used;
         // p = 2^(s * scale - m): the multiply-subtract and the row sum run two lanes at a time
         const uint64_t scale2 = pack2(p.scale_log2e, p.scale_log2e), nmsub2 = pack2(-msub, -msub);
         uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {  // P is packed in place: s[c] <- (p[2c], p[2c+1])
+        for (int c = 0; c < 16; ++c) {  // P is packed in place: s[c] <- (p[2c], p[2c+1])
           float a0, a1;
           unpack2(fma2(pack2(__uint_as_float(s[2 * c]), __uint_as_float(s[2 * c + 1])), scale2, nmsub2), a0, a1);
           const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
           sum2[c & 1] = add2(sum2[c & 1], pack2(p0, p1));
           s[c] = pack_bf16x2(p0, p1);
+        }
+        if (epi && OCH > 2) {
+          tmem_wait_ld();
+          epilogue_chunk(2, ob);
+        }
+#pragma unroll
+        for (int c = 16; c < 32; ++c) {
+          float a0, a1;
+          unpack2(fma2(pack2(__uint_as_float(s[2 * c]), __uint_as_float(s[2 * c + 1])), scale2, nmsub2), a0, a1);
+          const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
+          sum2[c & 1] = add2(sum2[c & 1], pack2(p0, p1));
+          s[c] = pack_bf16x2(p0, p1);
+        }
+        if (epi && OCH > 3) {
+          tmem_wait_ld();
+          epilogue_chunk(3, ob);
+        }
+        if (epi) {
+          pend = false;
+          PROF(5);  // (softmax of this tile and) the previous item's epilogue
         }
         {
           float t0, t1, t2, t3;
@@ -446,51 +536,27 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
       }
       if (!ok) break;
       T += x.n_kv;
-
-      // epilogue: O / l -> bf16; 32 columns at a time through this warp's patch of shared memory
-      if (!(ok = wait_or_abort(bar(PV_DONE0 + ((T - 1) & 1)), ((T - 1) >> 1) & 1, abort_flag))) break;
-      PROF(4);  // waiting for the last product before the epilogue
-      tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      // lane -> (row, 16-byte piece) of the eight 64-byte row segments one store instruction writes
-      const int srow = lane >> 2, spiece = lane & 3;
-      __nv_bfloat16* out_tile = p.out + static_cast<int64_t>(x.q0 + x.m0) * p.out_stride + x.h * D;
-      const int toks_valid = min(BMT, x.Lq - x.m0);
-      uint32_t ob[2][32];  // the load of the next 32 columns runs under the stores of the current ones
-      tmem_ld32(tmem_o + lane_addr, ob[0]);
+      // this item's epilogue: during the next item's first tile (or after the loop if none follows)
+      pend = true;
+      pend_inv = l > 0.f ? 1.f / l : 0.f;
+      pend_out = p.out + static_cast<int64_t>(x.q0 + x.m0) * p.out_stride + x.h * D;
+      pend_toks = min(BMT, x.Lq - x.m0);
+      pend_t = T - 1;
+      if (lane == 0) mbar_arrive(bar(ITEM_FREE0 + (it & 1)));  // the item's descriptor is in registers
+    }
+    if (ok && pend) {  // the block's last item
+      if ((ok = wait_or_abort(bar(PV_DONE0 + (pend_t & 1)), (pend_t >> 1) & 1, abort_flag))) {
+        PROF(4);
+        tc_fence_after();
+        uint32_t ob[32];
+        tmem_ld32(tmem_o + lane_addr, ob);
 #pragma unroll
-      for (int c = 0; c < OCH; ++c) {
-        uint32_t(&o)[32] = ob[c & 1];
-        tmem_wait_ld();
-        if (c + 1 < OCH) tmem_ld32(tmem_o + lane_addr + (c + 1) * 32, ob[(c + 1) & 1]);
-        if (c == OCH - 1) {  // O is in registers: the next item's first product may overwrite it
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(O_FREE));
+        for (int c = 0; c < OCH; ++c) {
+          tmem_wait_ld();
+          epilogue_chunk(c, ob);
         }
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          uint4 v;
-          v.x = pack_bf16x2(__uint_as_float(o[8 * k]) * inv, __uint_as_float(o[8 * k + 1]) * inv);
-          v.y = pack_bf16x2(__uint_as_float(o[8 * k + 2]) * inv, __uint_as_float(o[8 * k + 3]) * inv);
-          v.z = pack_bf16x2(__uint_as_float(o[8 * k + 4]) * inv, __uint_as_float(o[8 * k + 5]) * inv);
-          v.w = pack_bf16x2(__uint_as_float(o[8 * k + 6]) * inv, __uint_as_float(o[8 * k + 7]) * inv);
-          *reinterpret_cast<uint4*>(stage + lane * 64 + ((k ^ ((lane >> 1) & 3)) << 4)) = v;
-        }
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int lr = i * 8 + srow;       // row within the warp's 32
-          const int row = warp * 32 + lr;    // row of the tile
-          const int tok = row / pack, hh = row - tok * pack;
-          const uint4 v = *reinterpret_cast<const uint4*>(stage + lr * 64 + ((spiece ^ ((lr >> 1) & 3)) << 4));
-          if (tok < toks_valid)
-            *reinterpret_cast<uint4*>(out_tile + static_cast<int64_t>(tok) * p.out_stride + hh * D + c * 32 + spiece * 8) = v;
-        }
-        __syncwarp();
+        PROF(5);
       }
-      if (lane == 0) mbar_arrive(bar(ITEM_FREE0 + (it & 1)));
-      PROF(5);  // epilogue
     }
 #ifdef NVLLM_PREFILL_PROFILE
     if (tid == 0 && blockIdx.x < 2048)
@@ -525,6 +591,7 @@ static int launch_prefill_tcp_t(const PrefillParams& p_in, int64_t total_q, int6
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return fail(NVLLM_E_NO_DEVICE, "prefill: device index %d out of range", dev);
+  if (p_in.out_stride > (1 << 23)) return fail(NVLLM_E_GEOMETRY, "prefill: out row stride %lld too large", (long long)p_in.out_stride);
   if (!attr_done[dev]) {
     cudaError_t e = cudaFuncSetAttribute(prefill_tcp_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM);
     if (e != cudaSuccess) return fail(NVLLM_E_CUDA, "prefill (persistent): set-up failed: %s", cudaGetErrorString(e));
