@@ -252,6 +252,23 @@ NVLLM_API int nvllm_sample_tokens(const void* logits, int32_t logits_are_fp32, i
                         void* stream);
 
 /*
+ * The same pass for tensor-parallel ranks that each hold the logits of one slice of the
+ * vocabulary [vocab_offset, vocab_offset + vocab): instead of a token, row b yields
+ * candidates[b], one int64 that packs the slice's best (score, global index) so that a signed MAX
+ * over the ranks' candidates selects the token nvllm_sample_tokens would select from the
+ * concatenated row (same seed and step on every rank; the generated noise depends on the global
+ * index only).  nvllm_sample_unpack turns merged candidates into token ids.  Together with an
+ * 8-byte-per-row MAX reduction they stand where ParallelLMHead.forward gathers every rank's
+ * [batch, vocab / ranks] logits on rank 0 and concatenates them
+ * (nanovllm/layers/embed_head.py:78-87) before Sampler.forward (nanovllm/layers/sampler.py:10-26).
+ */
+NVLLM_API int nvllm_sample_candidates(const void* logits, int32_t logits_are_fp32, int64_t row_stride,
+                            const float* temperatures, const float* exponential_noise, int64_t noise_row_stride,
+                            uint64_t seed, uint64_t step, int64_t vocab_offset, int64_t* candidates,
+                            int32_t batch, int32_t vocab, void* stream);
+NVLLM_API int nvllm_sample_unpack(const int64_t* candidates, int64_t* tokens, int32_t batch, void* stream);
+
+/*
  * Decode-step inputs for a captured CUDA graph, in one launch.  `staged` is a device copy of
  * one host staging block holding, at the given BYTE offsets: tokens int64[batch] (last token of
  * each sequence), lens int32[batch] (sequence lengths, the new token included), offsets

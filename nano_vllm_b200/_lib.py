@@ -37,6 +37,9 @@ SIGNATURES = {
                                            c_void_p]),
     "nvllm_sample_tokens": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_uint64, c_uint64,
                                       c_void_p, c_int32, c_int32, c_void_p]),
+    "nvllm_sample_candidates": (c_int32, [c_void_p, c_int32, c_int64, c_void_p, c_void_p, c_int64, c_uint64, c_uint64,
+                                          c_int64, c_void_p, c_int32, c_int32, c_void_p]),
+    "nvllm_sample_unpack": (c_int32, [c_void_p, c_void_p, c_int32, c_void_p]),
     "nvllm_decode_step_inputs": (c_int32, [c_void_p, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32, c_int32, c_int32,
                                            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
     "nvllm_ar_handle_bytes": (c_int64, []),

@@ -307,6 +307,43 @@ def sample_tokens(logits: torch.Tensor, temperatures: torch.Tensor, noise: torch
     return out
 
 
+def sample_candidates(logits: torch.Tensor, temperatures: torch.Tensor, vocab_offset: int, noise: torch.Tensor | None = None,
+                      seed: int = 0, step: int = 0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``sample_tokens`` for one rank's slice ``[B, V / ranks]`` of the vocabulary, starting at global
+    index ``vocab_offset``: returns int64 ``[B]`` candidates whose element-wise maximum over the ranks
+    (``dist.reduce(..., op=MAX)``) decodes, with ``sample_unpack``, to the token ``sample_tokens``
+    picks from the concatenated logits.  Replaces the gather + cat of
+    nanovllm/layers/embed_head.py:78-87 by 8 bytes per row."""
+    assert logits.is_cuda and logits.dim() == 2 and logits.stride(-1) == 1
+    assert logits.dtype in (torch.bfloat16, torch.float32), f"logits must be bf16 or fp32, got {logits.dtype}"
+    B, V = logits.shape
+    assert temperatures.is_cuda and temperatures.dtype == torch.float32 and temperatures.numel() == B
+    assert temperatures.is_contiguous()
+    if noise is not None:
+        assert noise.is_cuda and noise.dtype == torch.float32 and noise.shape == logits.shape and noise.stride(-1) == 1
+    if out is None:
+        out = torch.empty(B, dtype=torch.int64, device=logits.device)
+    else:
+        assert out.is_cuda and out.dtype == torch.int64 and out.numel() == B and out.is_contiguous()
+    with torch.cuda.device(logits.device):
+        _lib.check(_lib.load().nvllm_sample_candidates(
+            logits.data_ptr(), 1 if logits.dtype == torch.float32 else 0, logits.stride(0), temperatures.data_ptr(),
+            noise.data_ptr() if noise is not None else None, noise.stride(0) if noise is not None else 0,
+            seed & 0xFFFFFFFFFFFFFFFF, step & 0xFFFFFFFFFFFFFFFF, int(vocab_offset), out.data_ptr(), B, V, _stream(logits)))
+    return out
+
+
+def sample_unpack(candidates: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Token ids int64 ``[B]`` of (merged) candidates from ``sample_candidates``."""
+    assert candidates.is_cuda and candidates.dtype == torch.int64 and candidates.is_contiguous()
+    B = candidates.numel()
+    if out is None:
+        out = torch.empty(B, dtype=torch.int64, device=candidates.device)
+    with torch.cuda.device(candidates.device):
+        _lib.check(_lib.load().nvllm_sample_unpack(candidates.data_ptr(), out.data_ptr(), B, _stream(candidates)))
+    return out
+
+
 # ---- the layer --------------------------------------------------------------------------
 
 class Attention(nn.Module):

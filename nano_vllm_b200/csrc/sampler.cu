@@ -21,6 +21,15 @@
 // SMs); 16-byte loads, four in flight per thread.  Each block reduces to one candidate, block 0
 // of the cluster collects the others' candidates from their shared memory.  Ties go to the
 // lowest index.
+//
+// Tensor parallelism: nano-vllm's LM head leaves every rank with the logits of its own slice of
+// the vocabulary and then gathers all slices on rank 0 and concatenates them
+// (nanovllm/layers/embed_head.py:78-87) before it samples.  The candidate form of this kernel
+// makes that traffic unnecessary: every rank reduces its slice to one (score, global index)
+// candidate per row, packed into an int64 whose signed order is "higher score first, then lower
+// index"; a MAX over the ranks (8 bytes per row) then picks the token that the one-rank kernel
+// would have picked from the concatenated row, because the noise is generated from the global
+// index.  nvllm_sample_unpack turns the winning candidates into token ids.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -34,9 +43,18 @@ struct SampleParams {
   const float* noise;  // nullable
   int64_t noise_stride;
   uint64_t seed, step;
-  int64_t* tokens;
-  int vocab;
+  int64_t* tokens;          // token ids, or packed candidates when `candidates` is set
+  int vocab;                // elements in a row of `logits`
+  int64_t offset;           // global vocabulary index of element 0 of a row
+  int candidates;
 };
+
+// (score, index) as one int64 that orders like "higher score, then lower index".
+__device__ __forceinline__ long long pack_candidate(float score, int idx) {
+  int s = __float_as_int(score);
+  s = s >= 0 ? s : s ^ 0x7fffffff;  // order-preserving map of float bits to a signed integer
+  return (static_cast<long long>(s) << 32) | static_cast<long long>(0xffffffffu - static_cast<unsigned int>(idx));
+}
 
 // Philox4x32 with 10 rounds (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11).
 __device__ __forceinline__ uint4 philox4x32_10(uint4 ctr, uint2 key) {
@@ -127,7 +145,10 @@ __global__ void __launch_bounds__(256, NVLLM_SAMPLER_MINBLOCKS) sample_kernel(co
     return s;
   };
 
-  const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+  // 16-byte loads need an aligned row, and a slice that starts on a group of four positions
+  // (one Philox call covers four consecutive global positions)
+  const int off = static_cast<int>(p.offset);
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(x) & 15u) == 0 && (off & 3) == 0;
   const int n_vec = vec_ok ? p.vocab / VEC : 0;
   auto consume = [&](const uint4& raw, int v) {
     const T* e = reinterpret_cast<const T*>(&raw);
@@ -136,14 +157,14 @@ __global__ void __launch_bounds__(256, NVLLM_SAMPLER_MINBLOCKS) sample_kernel(co
 #pragma unroll
       for (int h = 0; h < VEC / 4; ++h) {
         // counter: (group of 4 positions, row, step lo, step hi) -- unique per element and call
-        const uint4 r = philox4x32_10(make_uint4(static_cast<uint32_t>(v * (VEC / 4) + h), static_cast<uint32_t>(row),
+        const uint4 r = philox4x32_10(make_uint4(static_cast<uint32_t>((off >> 2) + v * (VEC / 4) + h), static_cast<uint32_t>(row),
                                                  static_cast<uint32_t>(p.step), static_cast<uint32_t>(p.step >> 32)),
                                       key);
         bits[4 * h] = r.x; bits[4 * h + 1] = r.y; bits[4 * h + 2] = r.z; bits[4 * h + 3] = r.w;
       }
     }
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) take_next(best, score_of(to_f32<T>(e[k]), v * VEC + k, bits[k]), v * VEC + k);
+    for (int k = 0; k < VEC; ++k) take_next(best, score_of(to_f32<T>(e[k]), v * VEC + k, bits[k]), off + v * VEC + k);
   };
   // four 16-byte loads in flight per thread before any of them is used
   constexpr int UNROLL = NVLLM_SAMPLER_UNROLL;
@@ -161,13 +182,14 @@ __global__ void __launch_bounds__(256, NVLLM_SAMPLER_MINBLOCKS) sample_kernel(co
   for (int i = n_vec * VEC + tid; i < p.vocab; i += nthreads) {
     uint32_t b = 0;
     if (!greedy && !nz) {
-      const uint4 r = philox4x32_10(make_uint4(static_cast<uint32_t>(i >> 2), static_cast<uint32_t>(row),
+      const int gi = off + i;  // global position
+      const uint4 r = philox4x32_10(make_uint4(static_cast<uint32_t>(gi >> 2), static_cast<uint32_t>(row),
                                                static_cast<uint32_t>(p.step), static_cast<uint32_t>(p.step >> 32)),
                                     key);
       const uint32_t w[4] = {r.x, r.y, r.z, r.w};
-      b = w[i & 3];
+      b = w[gi & 3];
     }
-    take_next(best, score_of(to_f32<T>(x[i]), i, b), i);
+    take_next(best, score_of(to_f32<T>(x[i]), i, b), off + i);
   }
 
   // block argmax: shuffle inside a warp, shared memory across the warps; then across the cluster
@@ -209,11 +231,26 @@ __global__ void __launch_bounds__(256, NVLLM_SAMPLER_MINBLOCKS) sample_kernel(co
       best.idx = *cluster.map_shared_rank(&blk_idx, lt);
     }
     warp_reduce();
-    // a row of NaN / -inf only: token 0, like an argmax over equal values
-    if (lt == 0) p.tokens[row] = best.idx == 0x7fffffff ? 0 : best.idx;
+    // a row of NaN / -inf only: token 0, like an argmax over equal values (after the merge, for
+    // candidates: the sentinel index loses against any real candidate of another rank)
+    if (lt == 0) {
+      if (p.candidates) p.tokens[row] = pack_candidate(best.score, best.idx);
+      else p.tokens[row] = best.idx == 0x7fffffff ? 0 : best.idx;
+    }
   }
   cluster.sync();  // no block leaves while its shared memory may still be read
 }
+
+__global__ void sample_unpack_kernel(const long long* packed, int64_t* tokens, int batch) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= batch) return;
+  const unsigned int idx = 0xffffffffu - static_cast<unsigned int>(packed[b] & 0xffffffffll);
+  tokens[b] = idx == 0x7fffffffu ? 0 : static_cast<int64_t>(idx);
+}
+
+static int sample_launch(const void* logits, int32_t logits_are_fp32, int64_t row_stride, const float* temperatures,
+                         const float* exponential_noise, int64_t noise_row_stride, uint64_t seed, uint64_t step,
+                         int64_t vocab_offset, int candidates, int64_t* tokens, int32_t batch, int32_t vocab, void* stream);
 
 }  // namespace nvllm
 
@@ -221,7 +258,38 @@ extern "C" int nvllm_sample_tokens(const void* logits, int32_t logits_are_fp32, 
                                    const float* temperatures, const float* exponential_noise, int64_t noise_row_stride,
                                    uint64_t seed, uint64_t step, int64_t* tokens, int32_t batch, int32_t vocab,
                                    void* stream) {
+  return nvllm::sample_launch(logits, logits_are_fp32, row_stride, temperatures, exponential_noise, noise_row_stride, seed, step,
+                              0, 0, tokens, batch, vocab, stream);
+}
+
+extern "C" int nvllm_sample_candidates(const void* logits, int32_t logits_are_fp32, int64_t row_stride,
+                                       const float* temperatures, const float* exponential_noise, int64_t noise_row_stride,
+                                       uint64_t seed, uint64_t step, int64_t vocab_offset, int64_t* candidates, int32_t batch,
+                                       int32_t vocab, void* stream) {
   using namespace nvllm;
+  if (vocab_offset < 0 || vocab_offset + vocab > 0x7ffffffell)
+    return fail(NVLLM_E_GEOMETRY, "sample_candidates: vocab_offset=%lld invalid", (long long)vocab_offset);
+  return sample_launch(logits, logits_are_fp32, row_stride, temperatures, exponential_noise, noise_row_stride, seed, step,
+                       vocab_offset, 1, candidates, batch, vocab, stream);
+}
+
+extern "C" int nvllm_sample_unpack(const int64_t* candidates, int64_t* tokens, int32_t batch, void* stream) {
+  using namespace nvllm;
+  if (batch < 0) return fail(NVLLM_E_GEOMETRY, "sample_unpack: batch=%d invalid", batch);
+  if (batch == 0) return NVLLM_OK;
+  if (!candidates || !tokens) return fail(NVLLM_E_NULL, "sample_unpack: NULL pointer argument");
+  if (reinterpret_cast<uintptr_t>(candidates) % 8 || reinterpret_cast<uintptr_t>(tokens) % 8)
+    return fail(NVLLM_E_ALIGN, "sample_unpack: pointers must be 8-byte aligned");
+  sample_unpack_kernel<<<(batch + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const long long*>(candidates), tokens, batch);
+  count_launch();
+  return check_launch("sample_unpack launch");
+}
+
+namespace nvllm {
+static int sample_launch(const void* logits, int32_t logits_are_fp32, int64_t row_stride, const float* temperatures,
+                         const float* exponential_noise, int64_t noise_row_stride, uint64_t seed, uint64_t step,
+                         int64_t vocab_offset, int candidates, int64_t* tokens, int32_t batch, int32_t vocab, void* stream) {
   if (batch < 0 || vocab <= 0) return fail(NVLLM_E_GEOMETRY, "sample_tokens: batch=%d vocab=%d invalid", batch, vocab);
   if (batch == 0) return NVLLM_OK;
   if (!logits || !temperatures || !tokens) return fail(NVLLM_E_NULL, "sample_tokens: NULL pointer argument");
@@ -241,6 +309,8 @@ extern "C" int nvllm_sample_tokens(const void* logits, int32_t logits_are_fp32, 
   p.step = step;
   p.tokens = tokens;
   p.vocab = vocab;
+  p.offset = vocab_offset;
+  p.candidates = candidates;
   // rows whose start is not 16-byte aligned take the element-wise path inside the kernel.
   // Blocks per row: as many (1, 2, 4, 8) as keep the grid within one resident wave of
   // 8 blocks on every SM of this device, and no more than the row has work for.
@@ -269,3 +339,4 @@ extern "C" int nvllm_sample_tokens(const void* logits, int32_t logits_are_fp32, 
   count_launch();
   return check_launch("sample_tokens launch");
 }
+}  // namespace nvllm

@@ -35,12 +35,13 @@ def staging_bytes(max_bs: int, table_width: int) -> int:
     return layout(max_bs)["blocks"] + 4 * max_bs * table_width
 
 
-def pack(seqs, buf: np.ndarray, with_temperatures: bool = True) -> tuple[int, int]:
+def pack(seqs, buf: np.ndarray, with_temperatures: bool = True, temperatures=None) -> tuple[int, int]:
     """Writes the step of ``seqs`` (objects with ``last_token``, ``num_tokens``, ``block_table``
     and, when ``with_temperatures``, ``temperature``: nanovllm/engine/sequence.py) into ``buf``
     (uint8).  Returns (bytes used, widest block table).  Tensor-parallel worker ranks pass
     ``with_temperatures=False``: the sequences they receive carry no sampling parameters
-    (Sequence.__getstate__, sequence.py:74-76) and only rank 0 samples."""
+    (Sequence.__getstate__, sequence.py:74-76) and only rank 0 samples -- unless the caller
+    hands the step's ``temperatures`` over as a list (the vocabulary-sharded sampling step)."""
     n = len(seqs)
     off = layout(n)
     counts = [len(s.block_table) for s in seqs]
@@ -50,7 +51,9 @@ def pack(seqs, buf: np.ndarray, with_temperatures: bool = True) -> tuple[int, in
         raise ValueError(f"staging block of {buf.size} bytes too small for {n} sequences with {total} blocks")
     buf[off["tokens"]:off["lens"]].view(np.int64)[:] = [s.last_token for s in seqs]
     buf[off["lens"]:off["temperatures"]].view(np.int32)[:] = [s.num_tokens for s in seqs]
-    if with_temperatures:
+    if temperatures is not None:
+        buf[off["temperatures"]:off["offsets"]].view(np.float32)[:] = temperatures
+    elif with_temperatures:
         buf[off["temperatures"]:off["offsets"]].view(np.float32)[:] = [s.temperature for s in seqs]
     offs = buf[off["offsets"]:off["blocks"]].view(np.int32)
     offs[0] = 0
@@ -73,7 +76,8 @@ class DecodeInputStager:
         self.turn = 0
         self.dev = torch.empty(nbytes, dtype=torch.uint8, device=device)
 
-    def stage(self, seqs, graph_bs: int, graph_vars: dict, with_temperatures: bool = True) -> torch.Tensor:
+    def stage(self, seqs, graph_bs: int, graph_vars: dict, with_temperatures: bool = True,
+              temperatures=None) -> torch.Tensor:
         """Fills rows [0, graph_bs) of ``graph_vars`` (the runner's static input tensors,
         model_runner.py:302-307) for a decode step of ``seqs``; returns the step's temperatures
         as a device tensor.  Everything is enqueued on the current stream."""
@@ -82,7 +86,7 @@ class DecodeInputStager:
         t = self.turn
         self.turn ^= 1
         self.copied[t].synchronize()  # returns at once unless that block's last copy is still running
-        end, widest = pack(seqs, self.host_np[t], with_temperatures)
+        end, widest = pack(seqs, self.host_np[t], with_temperatures, temperatures)
         end = (end + 15) // 16 * 16
         self.dev[:end].copy_(self.host[t][:end], non_blocking=True)
         self.copied[t].record()

@@ -89,6 +89,7 @@ def apply_shims(attn: str, ref_path: str):
             plugin.fuse_decode_inputs()
         if attn == "b200-full-ar":
             plugin.fuse_all_reduce()
+            plugin.fuse_lm_head()
     import nanovllm.engine.model_runner as mr
     mr.load_model = random_init
 
@@ -142,7 +143,7 @@ def main():
     ap.add_argument("--attn", default="b200", choices=["b200", "b200-fused", "b200-full", "b200-full-ar", "reference"],
                     help="b200: swap the attention layer; b200-fused: also fuse q/k norm + rotary + store; "
                          "b200-full: also the one-pass sampler and the one-launch decode inputs; b200-full-ar: also the "
-                         "peer-memory all-reduce (TP > 1); reference: stock nano-vllm")
+                         "peer-memory all-reduce and the vocabulary-sharded sampling (TP > 1); reference: stock nano-vllm")
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--model", default="qwen3-0.6b", choices=sorted(GEOMETRY))
     ap.add_argument("--num-seqs", type=int, default=256)

@@ -11,7 +11,8 @@ Optional steps after ``install()``, each replacing one method of the engine by a
 calls this package: ``fuse_pre_attention()`` (q/k norm + rotary + KV store in one launch),
 ``fuse_sampler()`` (one-pass token sampling), ``fuse_decode_inputs()`` (decode-step inputs in
 one copy and one launch) and, for tensor-parallel runs, ``fuse_all_reduce()`` (peer-memory sum
-behind the row-parallel projections).
+behind the row-parallel projections) and ``fuse_lm_head()`` (every rank samples its own slice of
+the vocabulary; 8 bytes per row travel instead of the logits).
 """
 from __future__ import annotations
 
@@ -70,40 +71,111 @@ def fuse_sampler(seed: int | None = None) -> None:
     sampler.Sampler.forward = forward
 
 
+# What the replacement of ModelRunner.run does; switched on by fuse_decode_inputs / fuse_lm_head.
+_runner = {"decode_inputs": False, "lm_head": False, "seed": 0, "step": 0, "stock_run": None}
+
+
+def _run(self, seqs, is_prefill, temperatures_list=None):
+    """ModelRunner.run (nanovllm/engine/model_runner.py:284-293) with the optional steps.  Rank 0 of
+    a tensor-parallel engine passes the step's temperatures along with the sequences when the
+    LM-head step is on (the pickled sequences carry no sampling parameters, sequence.py:74-76)."""
+    import torch
+    import torch.distributed as dist
+    ctx = importlib.import_module("nanovllm.utils.context")
+    lm = _runner["lm_head"] and self.world_size > 1
+    graphs = getattr(self, "graphs", None)
+    staged = (_runner["decode_inputs"] and not is_prefill and not self.enforce_eager and bool(graphs)
+              and len(seqs) <= self.graph_bs[-1])
+    if not staged and not lm:
+        return _runner["stock_run"](self, seqs, is_prefill)
+    if lm and temperatures_list is None:
+        temperatures_list = [seq.temperature for seq in seqs]  # rank 0
+    with torch.inference_mode():
+        if staged:
+            from .decode_inputs import DecodeInputStager
+            gv = self.graph_vars
+            stager = getattr(self, "_nvllm_stager", None)
+            if stager is None:
+                rows, width = gv["block_tables"].shape
+                stager = self._nvllm_stager = DecodeInputStager(rows, width, gv["block_tables"].device)
+            bs = len(seqs)
+            graph_bs = next(x for x in self.graph_bs if x >= bs)
+            temperatures = stager.stage(seqs, graph_bs, gv, temperatures=temperatures_list if lm else None,
+                                        with_temperatures=lm or self.rank == 0)
+            ctx.set_context(False, slot_mapping=gv["slot_mapping"][:bs], context_lens=gv["context_lens"][:bs],
+                            block_tables=gv["block_tables"][:bs])
+            graphs[graph_bs].replay()
+            logits = self.model.compute_logits(gv["outputs"][:bs])
+        else:
+            input_ids, positions = self.prepare_prefill(seqs) if is_prefill else self.prepare_decode(seqs)
+            temperatures = torch.tensor(temperatures_list, dtype=torch.float32, pin_memory=True).cuda(non_blocking=True)
+            logits = self.run_model(input_ids, positions, is_prefill)
+        if lm:
+            # every rank reduces its slice of the vocabulary to one candidate per row; a MAX over the
+            # ranks of 8 bytes per row replaces the gather + cat of the logits
+            _runner["step"] += 1
+            cand = _attention.sample_candidates(logits, temperatures, self.rank * logits.shape[1],
+                                                seed=_runner["seed"], step=_runner["step"])
+            dist.reduce(cand, dst=0, op=dist.ReduceOp.MAX)
+            token_ids = _attention.sample_unpack(cand).tolist() if self.rank == 0 else None
+        else:
+            token_ids = self.sampler(logits, temperatures).tolist() if self.rank == 0 else None
+    ctx.reset_context()
+    return token_ids
+
+
+def _install_run() -> None:
+    mr = importlib.import_module("nanovllm.engine.model_runner")
+    if _runner["stock_run"] is None:
+        _runner["stock_run"] = mr.ModelRunner.run
+        mr.ModelRunner.run = _run
+
+
 def fuse_decode_inputs() -> None:
     """Optional step: decode steps that replay a CUDA graph get their inputs through one staged
     copy and one launch (decode_inputs.DecodeInputStager) instead of ``prepare_decode`` /
     ``prepare_sample`` and the clear-and-copy in ``run_model``
     (nanovllm/engine/model_runner.py:218-258, 271-282).  Prefill steps, eager decode and batches
     beyond the captured sizes go through the stock ``ModelRunner.run``."""
-    import torch
+    _install_run()
+    _runner["decode_inputs"] = True
+
+
+def fuse_lm_head(seed: int = 0x5EED) -> None:
+    """Optional step for tensor-parallel runs: ``ParallelLMHead.forward``
+    (nanovllm/layers/embed_head.py:68-88) keeps every rank's slice of the logits where it is (no
+    ``dist.gather`` of ``[batch, vocab / ranks]`` per rank, no ``torch.cat`` on rank 0); every rank
+    runs the one-pass sampler over its slice (``sample_candidates``) and the ranks' candidates are
+    merged by one 8-byte-per-row MAX reduction.  Rank 0 sends the step's temperatures along with
+    the sequences (``ModelRunner.call``), since the workers' copies of the sequences carry none.
+    With one rank nothing changes.  Sampled rows use the generator of ``fuse_sampler`` keyed by
+    ``seed`` and counted by the number of steps, the same on every rank; greedy rows give the
+    reference's tokens."""
+    import torch.nn.functional as F
+    embed_head = importlib.import_module("nanovllm.layers.embed_head")
     mr = importlib.import_module("nanovllm.engine.model_runner")
     ctx = importlib.import_module("nanovllm.utils.context")
-    from .decode_inputs import DecodeInputStager
-    stock_run = mr.ModelRunner.run
+    _install_run()
+    _runner["lm_head"] = True
+    _runner["seed"] = seed
+    stock_forward = embed_head.ParallelLMHead.forward
+    stock_call = mr.ModelRunner.call
 
-    def run(self, seqs, is_prefill):
-        graphs = getattr(self, "graphs", None)
-        if is_prefill or self.enforce_eager or not graphs or len(seqs) > self.graph_bs[-1]:
-            return stock_run(self, seqs, is_prefill)
-        gv = self.graph_vars
-        stager = getattr(self, "_nvllm_stager", None)
-        if stager is None:
-            rows, width = gv["block_tables"].shape
-            stager = self._nvllm_stager = DecodeInputStager(rows, width, gv["block_tables"].device)
-        bs = len(seqs)
-        graph_bs = next(x for x in self.graph_bs if x >= bs)
-        with torch.inference_mode():
-            temperatures = stager.stage(seqs, graph_bs, gv, with_temperatures=self.rank == 0)
-            ctx.set_context(False, slot_mapping=gv["slot_mapping"][:bs], context_lens=gv["context_lens"][:bs],
-                            block_tables=gv["block_tables"][:bs])
-            graphs[graph_bs].replay()
-            logits = self.model.compute_logits(gv["outputs"][:bs])
-            token_ids = self.sampler(logits, temperatures).tolist() if self.rank == 0 else None
-        ctx.reset_context()
-        return token_ids
+    def forward(self, x):
+        if self.tp_size == 1:
+            return stock_forward(self, x)
+        context = ctx.get_context()
+        if context.is_prefill:  # only each sequence's last position is sampled (embed_head.py:72-74)
+            x = x[context.cu_seqlens_q[1:] - 1].contiguous()
+        return F.linear(x, self.weight, self.bias)  # this rank's slice of the vocabulary
 
-    mr.ModelRunner.run = run
+    def call(self, method_name, *args):
+        if method_name == "run" and self.world_size > 1 and self.rank == 0 and len(args) == 2:
+            args = (*args, [seq.temperature for seq in args[0]])
+        return stock_call(self, method_name, *args)
+
+    embed_head.ParallelLMHead.forward = forward
+    mr.ModelRunner.call = call
 
 
 def fuse_all_reduce(max_bytes: int = 8 << 20, wait_ms: int = 60000) -> None:
@@ -113,20 +185,30 @@ def fuse_all_reduce(max_bytes: int = 8 << 20, wait_ms: int = 60000) -> None:
     see PeerAllReduce.preferred), and with ``dist.all_reduce`` otherwise (prefill-sized tensors).  The peer mapping is made at the first
     call outside stream capture, which every rank reaches at the same point (the engine's warm-up
     forward).  Ranks of the engine run loosely coupled (a worker can be seconds behind while it
-    compiles or captures), hence the long default wait."""
+    compiles or captures), hence the long default wait.  A wait that does run out leaves a latch
+    in the kernel's buffers (later calls no longer wait and their sums are wrong) that only a
+    shutdown clears; every 256th eager call (prefill steps) therefore reads the device status
+    word and raises if the time-out bit is set, instead of generating on."""
     import torch
     import torch.distributed as dist
     import torch.nn.functional as F
     linear = importlib.import_module("nanovllm.layers.linear")
+    from . import _lib
     from .allreduce import PeerAllReduce
-    state = {"ar": None}
+    state = {"ar": None, "eager_calls": 0}
 
     def forward(self, x):
         y = F.linear(x, self.weight, self.bias if self.tp_rank == 0 else None)
         if self.tp_size > 1:
             ar = state["ar"]
-            if ar is None and not torch.cuda.is_current_stream_capturing():
+            capturing = torch.cuda.is_current_stream_capturing()
+            if ar is None and not capturing:
                 ar = state["ar"] = PeerAllReduce(dist.get_rank(), dist.get_world_size(), max_bytes, wait_ms=wait_ms)
+            if ar is not None and not capturing:
+                state["eager_calls"] += 1
+                if state["eager_calls"] % 256 == 0 and _lib.read_status() & 4:
+                    raise RuntimeError("nano_vllm_b200: a peer all-reduce gave up waiting for another rank "
+                                       "(NVLLM_STATUS_TIMEOUT); the sums since then are invalid")
             if ar is not None and ar.preferred(y):
                 ar.all_reduce(y)
             else:

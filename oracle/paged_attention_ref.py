@@ -169,6 +169,21 @@ def sampler_ref(logits, temperatures, noise):
     return sampler_scores_ref(logits, temperatures, noise).argmax(dim=-1)
 
 
+# ---- LM head + sampler under tensor parallelism (embed_head.py:68-88, sampler.py:10-26) -------
+
+def lm_head_sample_ref(hidden, weight_shards, cu_seqlens_q, temperatures, noise):
+    """Tokens of ``ParallelLMHead.forward`` followed by ``Sampler.forward``.  ``hidden`` [N, H];
+    ``weight_shards``: one [V / ranks, H] matrix per rank, in rank order.  Under prefill
+    (``cu_seqlens_q`` given) only each sequence's last row is kept (embed_head.py:72-74); every rank
+    multiplies by its shard (:77), rank 0 concatenates the ranks' logits along the vocabulary
+    (:78-87); the sampler then decides on the full rows with the given exponential draw."""
+    x = hidden
+    if cu_seqlens_q is not None:
+        x = x[(cu_seqlens_q[1:] - 1).to(torch.int64)].contiguous()
+    logits = torch.cat([F.linear(x, w) for w in weight_shards], dim=-1)
+    return sampler_ref(logits, temperatures, noise), logits
+
+
 # ---- decode-step inputs (nanovllm/engine/model_runner.py:151-159, 218-249, 271-282) ---------
 
 def decode_inputs_ref(seqs, graph_bs, table_width, block_size=BLOCK_SIZE):

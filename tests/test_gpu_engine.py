@@ -79,3 +79,11 @@ def test_tensor_parallel_engine_with_every_optional_step():
     d = _run("b200-full-ar", tp=2)
     assert d["lens"] == [40] * 10 and d["status"] == 0 and d["launches"] > 0
     assert d["same"] >= 0.9 * d["total"], d
+    # The vocabulary-sharded sampling tail (every rank reduces its slice of the logits to one
+    # candidate per row, 8 bytes per row are merged) must pick the tokens that rank 0 picks from
+    # the gathered and concatenated logits: greedy decoding, so token for token.  The two runs
+    # differ in the all-reduce as well (peer kernel and NCCL both sum in fp32, in rank order at
+    # two ranks), so a rare bf16 near-tie may still flip a token: nearly all must agree.
+    g = _run("b200-full", tp=2)
+    same = sum(a == b for x, y in zip(d["tokens"], g["tokens"]) for a, b in zip(x, y))
+    assert same >= 0.95 * d["total"] * 2, (same, d["total"])

@@ -5,11 +5,14 @@ import math
 import sys
 from pathlib import Path
 
+import numpy as np
 import pytest
 import torch
 
 sys.path.insert(0, str(Path(__file__).resolve().parent / "golden"))
 import cases as C  # noqa: E402
+
+GOLDEN = C.GOLDEN_DIR
 
 from nano_vllm_b200 import attention as A
 from oracle import paged_attention_ref as R
@@ -126,3 +129,61 @@ def test_bad_arguments_are_refused(cuda, lib):
     assert b"sample_tokens" in lib.nvllm_last_error()
     with pytest.raises(AssertionError):
         A.sample_tokens(logits.half(), t)
+
+
+# ---- vocabulary-sharded sampling (tensor-parallel LM head tail) ---------------------------------
+
+def _merge(cands):
+    """What dist.reduce(op=MAX) does over the ranks' candidate tensors."""
+    best = cands[0]
+    for c in cands[1:]:
+        best = torch.maximum(best, c)
+    return best
+
+
+def test_sharded_candidates_reproduce_the_reference_lm_head_and_sampler(cuda):
+    """nano-vllm's own ParallelLMHead + Sampler under 1, 2, 4, 8 emulated ranks
+    (tests/golden/lm_head.npz): every rank's slice of the logits goes through
+    nvllm_sample_candidates with the slice of the recorded draw, the candidates are merged by a
+    MAX, and the unpacked tokens must be the reference's (or tie with them to 1e-4 relative)."""
+    import sys
+    from pathlib import Path
+    sys.path.insert(0, str(Path(__file__).resolve().parent))
+    from test_oracle_golden import _lm_head_case
+    z = np.load(GOLDEN / "lm_head.npz")
+    for name in sorted({k.split(".")[0] for k in z.files}):
+        ranks, weight, x, cu, temps, noise = _lm_head_case(z, name)
+        want, logits = R.lm_head_sample_ref(x, list(weight.chunk(ranks, 0)), cu, temps, noise)
+        assert want.tolist() == z[f"{name}.tokens"].tolist()
+        per = logits.shape[1] // ranks
+        cands = []
+        for r in range(ranks):
+            sl = slice(r * per, (r + 1) * per)
+            cands.append(A.sample_candidates(logits[:, sl].contiguous().to(cuda), temps.to(cuda), r * per,
+                                             noise=noise[:, sl].contiguous().to(cuda)))
+        got = A.sample_unpack(_merge(cands)).cpu()
+        scores = R.sampler_scores_ref(logits, temps, noise)
+        for b in range(temps.numel()):
+            t, w = int(got[b]), int(want[b])
+            assert t == w or float(scores[b, t]) >= float(scores[b, w]) * (1 - 1e-4), f"{name} row {b}: {t} vs {w}"
+
+
+@pytest.mark.parametrize("ranks,vocab", [(2, 4096), (4, 6000), (8, 151936), (3, 1236), (2, 1002)])
+def test_sharded_candidates_pick_the_token_of_the_one_rank_kernel(cuda, ranks, vocab):
+    """Generated noise depends on (seed, step, row, global position) only, so slicing the
+    vocabulary must not change a single token: aligned slices, slices that do not start on a
+    group of four positions, greedy and sampled rows."""
+    g = torch.Generator().manual_seed(vocab + ranks)
+    logits = (torch.randn(7, vocab, generator=g) * 3).to(torch.bfloat16).to(cuda)
+    temps = torch.tensor([0.0, 0.6, 1.0, 0.0, 2.0, 0.3, 0.6], device=cuda)
+    per = vocab // ranks
+    for step in (1, 2, 99):
+        whole = A.sample_tokens(logits, temps, seed=5, step=step)
+        cands = [A.sample_candidates(logits[:, r * per:(r + 1) * per].contiguous(), temps, r * per, seed=5, step=step)
+                 for r in range(ranks)]
+        assert torch.equal(A.sample_unpack(_merge(cands)), whole)
+    # a slice with nothing to offer (all NaN) loses against any real candidate
+    nan_slice = torch.full((7, per), float("nan"), dtype=torch.bfloat16, device=cuda)
+    real = logits[:, :per].contiguous()
+    merged = _merge([A.sample_candidates(real, temps, 0, seed=5, step=1), A.sample_candidates(nan_slice, temps, per, seed=5, step=1)])
+    assert torch.equal(A.sample_unpack(merged), A.sample_tokens(real, temps, seed=5, step=1))

@@ -94,3 +94,32 @@ def test_pre_attention_oracle_matches_reference(name):
     assert torch.equal(q.view(torch.int16), c["q"].view(torch.int16))
     assert torch.equal(k.view(torch.int16), c["k"].view(torch.int16))
     assert torch.equal(v.reshape(v.shape[0], -1), c["qkv"][:, (c["hq"] + c["hkv"]) * c["d"]:])
+
+
+def _lm_head_case(z, name):
+    ranks, vocab, hidden, rows = (int(v) for v in z[f"{name}.shape"])
+    seed, noise_seed = (int(v) for v in z[f"{name}.seeds"])
+    g = torch.Generator().manual_seed(seed)
+    weight = torch.randn(vocab, hidden, generator=g).to(torch.bfloat16)
+    x = torch.randn(rows, hidden, generator=g).to(torch.bfloat16)
+    lens = z[f"{name}.lens"].tolist()
+    cu = torch.tensor([0] + list(np.cumsum(lens)), dtype=torch.int32) if lens else None
+    temps = torch.from_numpy(z[f"{name}.temperatures"])
+    torch.manual_seed(noise_seed)
+    noise = torch.empty(temps.numel(), vocab, dtype=torch.float32).exponential_(1)
+    return ranks, weight, x, cu, temps, noise
+
+
+def test_lm_head_and_sampler_oracle_reproduces_the_reference_under_emulated_ranks():
+    """oracle.lm_head_sample_ref against the tokens of nano-vllm's own ParallelLMHead + Sampler run
+    with 1, 2, 4 and 8 emulated ranks (tests/golden/make_lm_head_golden.py), prefill and decode."""
+    z = np.load(C.GOLDEN_DIR / "lm_head.npz")
+    names = sorted({k.split(".")[0] for k in z.files})
+    assert len(names) >= 6
+    for name in names:
+        ranks, weight, x, cu, temps, noise = _lm_head_case(z, name)
+        shards = list(weight.chunk(ranks, 0))
+        tokens, logits = R.lm_head_sample_ref(x, shards, cu, temps, noise)
+        assert tokens.tolist() == z[f"{name}.tokens"].tolist(), name
+        if f"{name}.logits" in z.files:
+            assert torch.equal(logits.view(torch.int16), torch.from_numpy(z[f"{name}.logits"])), name
