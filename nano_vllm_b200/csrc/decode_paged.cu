@@ -113,6 +113,7 @@ __global__ void __launch_bounds__(C::NW * 32, 2) decode_paged_kernel(const Decod
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_scan[NW];
   __shared__ int s_start[2];
+  __shared__ int s_last_arrival;
 
   pdl_prologue();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -324,37 +325,32 @@ __global__ void __launch_bounds__(C::NW * 32, 2) decode_paged_kernel(const Decod
       }
     }
     if (n_parts > 1) {  // block-uniform
-      // Only warp 0 waits for the counter: the other warps publish their share of the partial
-      // (fence), arrive on a named barrier and go back to streaming.
       __threadfence();
-      if (warp != 0) {
-        asm volatile("bar.arrive 1, %0;" ::"n"(NT) : "memory");
-      } else {
-        asm volatile("bar.sync 1, %0;" ::"n"(NT) : "memory");
-        unsigned int arrived = 0;
-        if (lane == 0) arrived = atomicAdd(&p.counters[cc.b * p.hkv + kvh], 1u);
-        arrived = __shfl_sync(0xffffffffu, arrived, 0);
-        if (arrived == static_cast<unsigned int>(n_parts - 1)) {  // every piece is in the workspace: merge in range order
-          __threadfence();
-          for (int idx = lane; idx < p.g * D; idx += 32) {
-            const int h = idx / D, d = idx % D;
-            const int head = kvh * p.g + h;
-            const int64_t row0 = static_cast<int64_t>(r_first + cc.b) * p.hq + head;
-            float mm = -INFINITY;
-            for (int j = 0; j < n_parts; ++j) mm = fmaxf(mm, __ldcg(p.ws_ml + (row0 + static_cast<int64_t>(j) * p.hq) * 2));
-            float L = 0.f, acc = 0.f;
-            for (int j = 0; j < n_parts; ++j) {
-              const int64_t row = row0 + static_cast<int64_t>(j) * p.hq;
-              const float mj = __ldcg(p.ws_ml + row * 2);
-              const float f = (mj == -INFINITY) ? 0.f : fast_exp2(mj - mm);
-              L += __ldcg(p.ws_ml + row * 2 + 1) * f;
-              acc += __ldcg(p.ws_o + row * D + d) * f;
-            }
-            p.out[cc.b * p.out_stride + static_cast<int64_t>(head) * D + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
+      __syncthreads();
+      if (tid == 0) {
+        const unsigned int arrived = atomicAdd(&p.counters[cc.b * p.hkv + kvh], 1u);
+        s_last_arrival = arrived == static_cast<unsigned int>(n_parts - 1);
+      }
+      __syncthreads();
+      if (s_last_arrival) {  // every piece is in the workspace: merge them in range order
+        __threadfence();
+        for (int idx = tid; idx < p.g * D; idx += NT) {
+          const int h = idx / D, d = idx % D;
+          const int head = kvh * p.g + h;
+          const int64_t row0 = static_cast<int64_t>(r_first + cc.b) * p.hq + head;
+          float mm = -INFINITY;
+          for (int j = 0; j < n_parts; ++j) mm = fmaxf(mm, __ldcg(p.ws_ml + (row0 + static_cast<int64_t>(j) * p.hq) * 2));
+          float L = 0.f, acc = 0.f;
+          for (int j = 0; j < n_parts; ++j) {
+            const int64_t row = row0 + static_cast<int64_t>(j) * p.hq;
+            const float mj = __ldcg(p.ws_ml + row * 2);
+            const float f = (mj == -INFINITY) ? 0.f : fast_exp2(mj - mm);
+            L += __ldcg(p.ws_ml + row * 2 + 1) * f;
+            acc += __ldcg(p.ws_o + row * D + d) * f;
           }
-          __syncwarp();
-          if (lane == 0) p.counters[cc.b * p.hkv + kvh] = 0u;  // ready for the next launch
+          p.out[cc.b * p.out_stride + static_cast<int64_t>(head) * D + d] = __float2bfloat16(L > 0.f ? acc / L : 0.f);
         }
+        if (tid == 0) p.counters[cc.b * p.hkv + kvh] = 0u;  // ready for the next launch
       }
     }
   };

@@ -28,11 +28,23 @@
 // 64-byte row segments.
 #include <atomic>
 #include <cstdlib>
+#include <type_traits>
 
 #include "common.cuh"
 #include "prefill.cuh"
 #include "prefill_tc.cuh"
 #include "sm100.cuh"
+
+// 1: an item's epilogue is carried into the next item's first key tile (see the softmax warps);
+// 0: it runs as soon as the item's last product is done (A/B builds).
+#ifndef NVLLM_PREFILL_CARRY
+#define NVLLM_PREFILL_CARRY 1
+#endif
+// 1: the S product of the next item's first key tile is issued before the current item's last
+// P V product; 0: after it (A/B builds).
+#ifndef NVLLM_PREFILL_LOOKAHEAD
+#define NVLLM_PREFILL_LOOKAHEAD 1
+#endif
 
 namespace nvllm {
 using namespace sm100;
@@ -307,36 +319,63 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
         umma_commit(bar(QK_DONE0 + st));
         return true;
       };
+      // The products form one stream over the block's key tiles, across items: S of tile t+1 is
+      // always issued before P V of tile t, so that it runs under tile t's softmax -- also when
+      // tile t+1 is the first tile of the NEXT item (its Q is loaded as soon as the current item's
+      // last S product has finished, well before the current item's last softmax ends).
       int T = 0, nq = 0;
       bool ok = true;
-      for (int it = 0; ok; ++it) {
-        if (!(ok = wait_or_abort(bar(ITEM_FULL0 + (it & 1)), (it >> 1) & 1, abort_flag))) break;
-        const Item x = read_item(it);
-        if (x.n_kv < 0) break;
-        {
-          if (!(ok = wait_or_abort(bar(Q_FULL), nq & 1, abort_flag))) break;
+      Item x;
+      x.n_kv = -1;
+      if ((ok = wait_or_abort(bar(ITEM_FULL0), 0, abort_flag))) x = read_item(0);
+      if (ok && x.n_kv > 0) {
+        if ((ok = wait_or_abort(bar(Q_FULL), nq & 1, abort_flag))) {
           ++nq;
-          if (!(ok = issue_qk(T))) break;
-          for (int j = 0; j < x.n_kv; ++j) {
-            const int t = T + j, st = t & 1, ph = (t >> 1) & 1;
-            if (j + 1 < x.n_kv && !(ok = issue_qk(t + 1))) break;  // next S runs under this tile's softmax
-            if (!(ok = wait_or_abort(bar(V_FULL0 + st), ph, abort_flag))) break;
-            if (!(ok = wait_or_abort(bar(P_FULL0 + st), ph, abort_flag))) break;
-            // the first product of an item overwrites O: the previous item's O must have been read
-            if (j == 0 && it > 0 && !(ok = wait_or_abort(bar(O_FREE), (it - 1) & 1, abort_flag))) break;
-            tc_fence_after();
-            const uint64_t vd = v_desc + static_cast<uint64_t>(st * (KV_BYTES >> 4));
-            const uint32_t p_tmem = tmem + st * 64;
-#pragma unroll
-            for (int ks = 0; ks < BN / 16; ++ks)
-              umma_ts(tmem_o, p_tmem + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
-                      (j > 0 || ks > 0) ? 1u : 0u);
-            umma_commit(bar(PV_DONE0 + st));
-          }
-          if (!ok) break;
-          T += x.n_kv;
+          ok = issue_qk(T);
         }
+      }
+      for (int it = 0; ok && x.n_kv > 0; ++it) {
+        Item nx;
+        nx.n_kv = -1;
+        for (int j = 0; j < x.n_kv; ++j) {
+          const int t = T + j, st = t & 1, ph = (t >> 1) & 1;
+          if (j + 1 < x.n_kv) {
+            if (!(ok = issue_qk(t + 1))) break;  // next S runs under this tile's softmax
+          } else if (NVLLM_PREFILL_LOOKAHEAD) {
+            if (!(ok = wait_or_abort(bar(ITEM_FULL0 + ((it + 1) & 1)), ((it + 1) >> 1) & 1, abort_flag))) break;
+            nx = read_item(it + 1);
+            if (nx.n_kv > 0) {
+              if (!(ok = wait_or_abort(bar(Q_FULL), nq & 1, abort_flag))) break;
+              ++nq;
+              if (!(ok = issue_qk(t + 1))) break;  // the next item's first S
+            }
+          }
+          if (!(ok = wait_or_abort(bar(V_FULL0 + st), ph, abort_flag))) break;
+          if (!(ok = wait_or_abort(bar(P_FULL0 + st), ph, abort_flag))) break;
+          // the first product of an item overwrites O: the previous item's O must have been read
+          if (j == 0 && it > 0 && !(ok = wait_or_abort(bar(O_FREE), (it - 1) & 1, abort_flag))) break;
+          tc_fence_after();
+          const uint64_t vd = v_desc + static_cast<uint64_t>(st * (KV_BYTES >> 4));
+          const uint32_t p_tmem = tmem + st * 64;
+#pragma unroll
+          for (int ks = 0; ks < BN / 16; ++ks)
+            umma_ts(tmem_o, p_tmem + ks * 8, vd + static_cast<uint64_t>((ks * 2048) >> 4), idesc_pv,
+                    (j > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(bar(PV_DONE0 + st));
+        }
+        if (!ok) break;
+        T += x.n_kv;
         mbar_arrive(bar(ITEM_FREE0 + (it & 1)));
+        if (!NVLLM_PREFILL_LOOKAHEAD) {
+          if (!(ok = wait_or_abort(bar(ITEM_FULL0 + ((it + 1) & 1)), ((it + 1) >> 1) & 1, abort_flag))) break;
+          nx = read_item(it + 1);
+          if (nx.n_kv > 0) {
+            if (!(ok = wait_or_abort(bar(Q_FULL), nq & 1, abort_flag))) break;
+            ++nq;
+            if (!(ok = issue_qk(T))) break;
+          }
+        }
+        x = nx;
       }
       if (!ok) {  // make sure nothing is still running on TMEM before it is freed
         umma_commit(bar(DRAIN));
@@ -353,12 +392,14 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
     // lane -> (row, 16-byte piece).  The four rows a lane stores never change: token and head of
     // each, and its offset in the output, are worked out once.
     const int srow = lane >> 2, spiece = lane & 3;
-    int st_tok[4], st_off[4];  // a tile spans at most 128 output rows: the offsets fit 32 bits
+    int st_off[4];      // a tile spans at most 128 output rows: the offsets fit 32 bits
+    uint32_t st_toks = 0;  // the four rows' tokens within the tile, 8 bits each
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int row = warp * 32 + i * 8 + srow;  // row of the tile
-      st_tok[i] = row / pack;
-      st_off[i] = st_tok[i] * static_cast<int>(p.out_stride) + (row - st_tok[i] * pack) * D + spiece * 8;
+      const int tok = row / pack;
+      st_toks |= static_cast<uint32_t>(tok) << (8 * i);
+      st_off[i] = tok * static_cast<int>(p.out_stride) + (row - tok * pack) * D + spiece * 8;
     }
     // The epilogue of an item (O / l -> bf16 rows in the output) does not run when the item's last
     // product is done: it is carried into the first key tile of the NEXT item and done there 32
@@ -394,71 +435,84 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
       for (int i = 0; i < 4; ++i) {
         const int lr = i * 8 + srow;  // row within the warp's 32
         const uint4 v = *reinterpret_cast<const uint4*>(stage + lr * 64 + ((spiece ^ ((lr >> 1) & 3)) << 4));
-        if (st_tok[i] < pend_toks) *reinterpret_cast<uint4*>(pend_out + st_off[i] + c * 32) = v;
+        if (static_cast<int>((st_toks >> (8 * i)) & 0xffu) < pend_toks) *reinterpret_cast<uint4*>(pend_out + st_off[i] + c * 32) = v;
       }
       __syncwarp();
     };
     int T = 0;
     bool ok = true;
     PROF_DECL;
-    for (int it = 0; ok; ++it) {
-      if (!(ok = wait_or_abort(bar(ITEM_FULL0 + (it & 1)), (it >> 1) & 1, abort_flag))) break;
-      const Item x = read_item(it);
-      PROF(0);  // waiting for the next item
-      if (x.n_kv < 0) break;
-      PROF_COUNT(6);
-      const int qi = x.m0 + r_tok, off = x.Lk - x.Lq;
-      float m_used = -INFINITY, l = 0.f;
-      for (int j = 0; j < x.n_kv; ++j) {
-        const int t = T + j, st = t & 1, ph = (t >> 1) & 1;
-        const uint32_t tmem_s = tmem + st * 64 + lane_addr;
-        if (!(ok = wait_or_abort(bar(QK_DONE0 + st), ph, abort_flag))) break;
-        PROF(1);  // waiting for the scores
-        PROF_COUNT(7);
-        tc_fence_after();
-        uint32_t s[64];
-        tmem_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-        tmem_ld32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-        const bool epi = pend && j == 0;  // warp-uniform: the previous item's epilogue rides on this tile
-        uint32_t ob[32];
-        if (epi) {
-          if (!(ok = wait_or_abort(bar(PV_DONE0 + (pend_t & 1)), (pend_t >> 1) & 1, abort_flag))) break;
-          PROF(4);  // waiting for the previous item's last product
-          tc_fence_after();
-          tmem_ld32(tmem_o + lane_addr, ob);
-        }
+    // The pending epilogue on its own (the block's last item).
+    auto epilogue_now = [&]() -> bool {
+      if (!wait_or_abort(bar(PV_DONE0 + (pend_t & 1)), (pend_t >> 1) & 1, abort_flag)) return false;
+      PROF(4);
+      tc_fence_after();
+      uint32_t ob[32];
+      tmem_ld32(tmem_o + lane_addr, ob);
+#pragma unroll
+      for (int c = 0; c < OCH; ++c) {
         tmem_wait_ld();
-        if (epi) epilogue_chunk(0, ob);
+        epilogue_chunk(c, ob);
+      }
+      PROF(5);
+      pend = false;
+      return true;
+    };
+    // One key tile of an item: scores -> P.  Two compiled variants: the plain one, and the one for
+    // an item's first tile that also carries the previous item's epilogue (kept apart so that the
+    // plain tile does not pay for the epilogue's registers).  Returns false when a wait gave up.
+    auto do_tile = [&](auto carries_epilogue, const Item& x, int j, float& m_used, float& l) -> bool {
+      constexpr bool EPI = decltype(carries_epilogue)::value;
+      const int qi = x.m0 + r_tok, off = x.Lk - x.Lq;
+      const int t = T + j, st = t & 1, ph = (t >> 1) & 1;
+      const uint32_t tmem_s = tmem + st * 64 + lane_addr;
+      if (!wait_or_abort(bar(QK_DONE0 + st), ph, abort_flag)) return false;
+      PROF(1);  // waiting for the scores
+      PROF_COUNT(7);
+      tc_fence_after();
+      uint32_t s[64];
+      tmem_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_ld32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+      uint32_t ob[EPI ? 32 : 1];
+      if constexpr (EPI) {
+        if (!wait_or_abort(bar(PV_DONE0 + (pend_t & 1)), (pend_t >> 1) & 1, abort_flag)) return false;
+        PROF(4);  // waiting for the previous item's last product
+        tc_fence_after();
+        tmem_ld32(tmem_o + lane_addr, ob);
+      }
+      tmem_wait_ld();
+      if constexpr (EPI) epilogue_chunk(0, ob);
 
-        const int j0 = j * BN;
-        if ((j0 + BN - 1 > x.m0 + off) || (j0 + BN > x.Lk)) {  // tile touches the diagonal or the end
-          const int limit = min(qi + off, x.Lk - 1) - j0;        // columns c <= limit are visible
+      const int j0 = j * BN;
+      if ((j0 + BN - 1 > x.m0 + off) || (j0 + BN > x.Lk)) {  // tile touches the diagonal or the end
+        const int limit = min(qi + off, x.Lk - 1) - j0;        // columns c <= limit are visible
 #pragma unroll
-          for (int c = 0; c < 64; ++c)
-            if (c > limit) s[c] = 0xff800000u;  // -inf
-        }
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        for (int c = 0; c < 64; ++c)
+          if (c > limit) s[c] = 0xff800000u;  // -inf
+      }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 64; c += 8) {
-          mx4[0] = fmax3(mx4[0], __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
-          mx4[1] = fmax3(mx4[1], __uint_as_float(s[c + 2]), __uint_as_float(s[c + 3]));
-          mx4[2] = fmax3(mx4[2], __uint_as_float(s[c + 4]), __uint_as_float(s[c + 5]));
-          mx4[3] = fmax3(mx4[3], __uint_as_float(s[c + 6]), __uint_as_float(s[c + 7]));
+      for (int c = 0; c < 64; c += 8) {
+        mx4[0] = fmax3(mx4[0], __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
+        mx4[1] = fmax3(mx4[1], __uint_as_float(s[c + 2]), __uint_as_float(s[c + 3]));
+        mx4[2] = fmax3(mx4[2], __uint_as_float(s[c + 4]), __uint_as_float(s[c + 5]));
+        mx4[3] = fmax3(mx4[3], __uint_as_float(s[c + 6]), __uint_as_float(s[c + 7]));
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      const float m_new = fmaxf(m_used, mx * p.scale_log2e);
+      // lazy rescale: keep the old reference maximum unless it has been outgrown by 2^8
+      const bool grow = m_new > m_used + kRescaleThreshold;
+      if (__any_sync(0xffffffffu, grow)) {
+        float alpha = 1.f;
+        if (grow) {
+          alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
+          m_used = m_new;
+          l *= alpha;
         }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        const float m_new = fmaxf(m_used, mx * p.scale_log2e);
-        // lazy rescale: keep the old reference maximum unless it has been outgrown by 2^8
-        const bool grow = m_new > m_used + kRescaleThreshold;
-        if (__any_sync(0xffffffffu, grow)) {
-          float alpha = 1.f;
-          if (grow) {
-            alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
-            m_used = m_new;
-            l *= alpha;
-          }
+        if constexpr (!EPI) {
           if (j > 0) {  // O holds tiles 0..j-1 of this item once the previous P V product has finished
             PROF(2);
-            if (!(ok = wait_or_abort(bar(PV_DONE0 + ((t - 1) & 1)), ((t - 1) >> 1) & 1, abort_flag))) break;
+            if (!wait_or_abort(bar(PV_DONE0 + ((t - 1) & 1)), ((t - 1) >> 1) & 1, abort_flag)) return false;
             PROF(3);  // waiting for O before a rescale
             tc_fence_after();
 #pragma unroll
@@ -472,68 +526,82 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
             }
           }
         }
-        if (epi && OCH > 1) {
-          tmem_wait_ld();
-          epilogue_chunk(1, ob);
-        }
-        const float msub = (m_used == -INFINITY) ? 0.f : m_used;
-        // p = 2^(s * scale - m): the multiply-subtract and the row sum run two lanes at a time
-        const uint64_t scale2 = pack2(p.scale_log2e, p.scale_log2e), nmsub2 = pack2(-msub, -msub);
-        uint64_t sum2[2] = {0ull, 0ull};
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {  // P is packed in place: s[c] <- (p[2c], p[2c+1])
-          float a0, a1;
-          unpack2(fma2(pack2(__uint_as_float(s[2 * c]), __uint_as_float(s[2 * c + 1])), scale2, nmsub2), a0, a1);
-          const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
-          sum2[c & 1] = add2(sum2[c & 1], pack2(p0, p1));
-          s[c] = pack_bf16x2(p0, p1);
-        }
-        if (epi && OCH > 2) {
-          tmem_wait_ld();
-          epilogue_chunk(2, ob);
-        }
-#pragma unroll
-        for (int c = 16; c < 32; ++c) {
-          float a0, a1;
-          unpack2(fma2(pack2(__uint_as_float(s[2 * c]), __uint_as_float(s[2 * c + 1])), scale2, nmsub2), a0, a1);
-          const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
-          sum2[c & 1] = add2(sum2[c & 1], pack2(p0, p1));
-          s[c] = pack_bf16x2(p0, p1);
-        }
-        if (epi && OCH > 3) {
-          tmem_wait_ld();
-          epilogue_chunk(3, ob);
-        }
-        if (epi) {
-          pend = false;
-          PROF(5);  // (softmax of this tile and) the previous item's epilogue
-        }
-        {
-          float t0, t1, t2, t3;
-          unpack2(sum2[0], t0, t1);
-          unpack2(sum2[1], t2, t3);
-          l += (t0 + t1) + (t2 + t3);
-        }
-        if (j0 + BN > x.Lk) {
-          // Last tile of the sequence: V rows past the end hold whatever the cache block (or the
-          // next sequence) has there.  Their P is 0, but 0 x NaN would still poison O, so the
-          // rows are cleared in shared memory before the product is issued.
-          if (!(ok = wait_or_abort(bar(V_FULL0 + st), ph, abort_flag))) break;
-          const int first = x.Lk - j0;  // rows [first, 64) are dead
-          unsigned char* vt = base_ptr + OFF_V + st * KV_BYTES;
-          for (int i = r; i < (BN - first) * PIECES; i += 128) {
-            const int row = first + i / PIECES, piece = i % PIECES;
-            *reinterpret_cast<uint4*>(vt + (piece >> 3) * KV_SUB + row * 128 + (piece & 7) * 16) = make_uint4(0, 0, 0, 0);
-          }
-          fence_proxy_async();
-        }
-        tmem_st32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(P_FULL0 + st));
-        PROF(2);  // softmax of one tile
       }
+      if constexpr (EPI && OCH > 1) {
+        tmem_wait_ld();
+        epilogue_chunk(1, ob);
+      }
+      const float msub = (m_used == -INFINITY) ? 0.f : m_used;
+      // p = 2^(s * scale - m): the multiply-subtract and the row sum run two lanes at a time
+      const uint64_t scale2 = pack2(p.scale_log2e, p.scale_log2e), nmsub2 = pack2(-msub, -msub);
+      uint64_t sum2[2] = {0ull, 0ull};
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {  // P is packed in place: s[c] <- (p[2c], p[2c+1])
+        float a0, a1;
+        unpack2(fma2(pack2(__uint_as_float(s[2 * c]), __uint_as_float(s[2 * c + 1])), scale2, nmsub2), a0, a1);
+        const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
+        sum2[c & 1] = add2(sum2[c & 1], pack2(p0, p1));
+        s[c] = pack_bf16x2(p0, p1);
+      }
+      if constexpr (EPI && OCH > 2) {
+        tmem_wait_ld();
+        epilogue_chunk(2, ob);
+      }
+#pragma unroll
+      for (int c = 16; c < 32; ++c) {
+        float a0, a1;
+        unpack2(fma2(pack2(__uint_as_float(s[2 * c]), __uint_as_float(s[2 * c + 1])), scale2, nmsub2), a0, a1);
+        const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
+        sum2[c & 1] = add2(sum2[c & 1], pack2(p0, p1));
+        s[c] = pack_bf16x2(p0, p1);
+      }
+      if constexpr (EPI && OCH > 3) {
+        tmem_wait_ld();
+        epilogue_chunk(3, ob);
+      }
+      if constexpr (EPI) PROF(5);  // (softmax of this tile and) the previous item's epilogue
+      {
+        float t0, t1, t2, t3;
+        unpack2(sum2[0], t0, t1);
+        unpack2(sum2[1], t2, t3);
+        l += (t0 + t1) + (t2 + t3);
+      }
+      if (j0 + BN > x.Lk) {
+        // Last tile of the sequence: V rows past the end hold whatever the cache block (or the
+        // next sequence) has there.  Their P is 0, but 0 x NaN would still poison O, so the
+        // rows are cleared in shared memory before the product is issued.
+        if (!wait_or_abort(bar(V_FULL0 + st), ph, abort_flag)) return false;
+        const int first = x.Lk - j0;  // rows [first, 64) are dead
+        unsigned char* vt = base_ptr + OFF_V + st * KV_BYTES;
+        for (int i = r; i < (BN - first) * PIECES; i += 128) {
+          const int row = first + i / PIECES, piece = i % PIECES;
+          *reinterpret_cast<uint4*>(vt + (piece >> 3) * KV_SUB + row * 128 + (piece & 7) * 16) = make_uint4(0, 0, 0, 0);
+        }
+        fence_proxy_async();
+      }
+      tmem_st32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(P_FULL0 + st));
+      PROF(2);  // softmax of one tile
+      return true;
+    };
+    for (int it = 0; ok; ++it) {
+      if (!(ok = wait_or_abort(bar(ITEM_FULL0 + (it & 1)), (it >> 1) & 1, abort_flag))) break;
+      const Item x = read_item(it);
+      PROF(0);  // waiting for the next item
+      if (x.n_kv < 0) break;
+      PROF_COUNT(6);
+      float m_used = -INFINITY, l = 0.f;
+      int j = 0;
+      if (NVLLM_PREFILL_CARRY && pend) {  // warp-uniform: the previous item's epilogue rides on this item's first tile
+        if (!(ok = do_tile(std::true_type{}, x, 0, m_used, l))) break;
+        pend = false;
+        j = 1;
+      }
+      for (; j < x.n_kv; ++j)
+        if (!(ok = do_tile(std::false_type{}, x, j, m_used, l))) break;
       if (!ok) break;
       T += x.n_kv;
       // this item's epilogue: during the next item's first tile (or after the loop if none follows)
@@ -543,21 +611,9 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
       pend_toks = min(BMT, x.Lq - x.m0);
       pend_t = T - 1;
       if (lane == 0) mbar_arrive(bar(ITEM_FREE0 + (it & 1)));  // the item's descriptor is in registers
+      if (!NVLLM_PREFILL_CARRY && !(ok = epilogue_now())) break;
     }
-    if (ok && pend) {  // the block's last item
-      if ((ok = wait_or_abort(bar(PV_DONE0 + (pend_t & 1)), (pend_t >> 1) & 1, abort_flag))) {
-        PROF(4);
-        tc_fence_after();
-        uint32_t ob[32];
-        tmem_ld32(tmem_o + lane_addr, ob);
-#pragma unroll
-        for (int c = 0; c < OCH; ++c) {
-          tmem_wait_ld();
-          epilogue_chunk(c, ob);
-        }
-        PROF(5);
-      }
-    }
+    if (ok && pend) ok = epilogue_now();  // the block's last item
 #ifdef NVLLM_PREFILL_PROFILE
     if (tid == 0 && blockIdx.x < 2048)
       for (int i = 0; i < 8; ++i) g_prefill_prof[blockIdx.x * 8 + i] = prof[i];
