@@ -197,10 +197,10 @@ NVLLM_API int nvllm_decode_paged_static(const void* q, int64_t q_row_stride,
  * total_q / total_k are the row counts of q and of packed k/v (ignored for k/v in paged
  * mode); they bound the tiled loads, nothing past them is read.
  * Cache contents past a sequence's length are never observed (stale NaN/Inf cannot leak).
- * Supported: D in {64,128}; Hq % Hkv == 0.  Runs on the persistent tcgen05 kernel (batch <= 1024;
- * larger batches fall back to the one-block-per-tile tcgen05 kernel for D == 128 and to the
- * mma.sync kernel for D == 64).  The environment variable NVLLM_PREFILL_IMPL = mma | tc | tcp,
- * read on every call, forces one of them (measurement and test aid).
+ * Supported: D in {64,128}; Hq % Hkv == 0; batch <= 1024 (nano-vllm schedules at most 512
+ * sequences per step); more is rejected with NVLLM_E_GEOMETRY.  Runs on the persistent tcgen05
+ * kernel.  The environment variable NVLLM_PREFILL_IMPL=mma, read on every call, selects a
+ * warp-level mma.sync kernel instead (cross-check for tests and A/B baseline for measurements).
  */
 NVLLM_API int nvllm_prefill_varlen(const void* q, int64_t q_row_stride,
                          const void* k, int64_t k_row_stride,

@@ -16,7 +16,7 @@ extern "C" int nvllm_prefill_varlen(const void* q, int64_t q_row_stride, const v
     return fail(NVLLM_E_GEOMETRY, "prefill_varlen: head_dim=%d unsupported (64 or 128)", head_dim);
   if (num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads)
     return fail(NVLLM_E_GEOMETRY, "prefill_varlen: Hq=%d must be a positive multiple of Hkv=%d", num_q_heads, num_kv_heads);
-  if (batch < 0 || batch > 65535 || num_q_heads > 65535)
+  if (batch < 0 || num_q_heads > 65535)
     return fail(NVLLM_E_GEOMETRY, "prefill_varlen: batch=%d / Hq=%d outside the launch limits", batch, num_q_heads);
   if (max_seqlen_q < 0 || max_seqlen_k < 0)
     return fail(NVLLM_E_GEOMETRY, "prefill_varlen: negative max_seqlen");
@@ -65,18 +65,13 @@ extern "C" int nvllm_prefill_varlen(const void* q, int64_t q_row_stride, const v
   p.pack = 1;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.num_blocks = num_blocks;
-  // NVLLM_PREFILL_IMPL = mma | tc | tcp picks a kernel by hand (measurement and test aid, read on
-  // every call); by default the persistent tcgen05 kernel runs whenever it can.
-  char impl = 'a';
-  if (const char* s = std::getenv("NVLLM_PREFILL_IMPL")) {
-    if (s[0] == 'm') impl = 'm';
-    else if (s[0] == 't' && s[1] == 'c' && s[2] == 'p') impl = 'p';
-    else if (s[0] == 't') impl = 't';
-  }
+  // The persistent tcgen05 kernel is the product.  NVLLM_PREFILL_IMPL=mma (read on every call)
+  // selects the warp-level mma.sync kernel instead: the cross-check of the tests and the A/B
+  // baseline of measurements, never chosen by the library itself.
+  const char* forced = std::getenv("NVLLM_PREFILL_IMPL");
   const bool has_rows = block_tables || total_k > 0;
-  if (impl != 'm' && impl != 't' && has_rows && batch <= 1024)
-    return launch_prefill_tcp(p, total_q, total_k, static_cast<cudaStream_t>(stream));
-  if (impl != 'm' && head_dim == 128 && has_rows)
-    return launch_prefill_tc(p, total_q, total_k, static_cast<cudaStream_t>(stream));
-  return launch_prefill_mma(p, static_cast<cudaStream_t>(stream));
+  if ((forced && forced[0] == 'm') || !has_rows) return launch_prefill_mma(p, static_cast<cudaStream_t>(stream));
+  if (batch > kPrefillMaxBatch)
+    return fail(NVLLM_E_GEOMETRY, "prefill_varlen: batch=%d exceeds the %d sequences of one launch", batch, kPrefillMaxBatch);
+  return launch_prefill_tcp(p, total_q, total_k, static_cast<cudaStream_t>(stream));
 }

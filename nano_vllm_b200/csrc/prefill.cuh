@@ -26,12 +26,15 @@ struct PrefillParams {
   int* status;
 };
 
-// Warp-level mma.sync kernel: every supported geometry.
+// Sequences per launch of the persistent kernel (its per-sequence tables live in shared memory).
+// The engine schedules at most 512 sequences per step (nanovllm/config.py:10).
+constexpr int kPrefillMaxBatch = 1024;
+
+// Warp-level mma.sync kernel: every supported geometry; cross-check and A/B baseline only
+// (batch <= 65535).
 int launch_prefill_mma(const PrefillParams& p, cudaStream_t stream);
-// tcgen05 / TMEM / TMA kernel: head_dim 128.  total_q / total_k bound the tiled loads.
-int launch_prefill_tc(const PrefillParams& p, int64_t total_q, int64_t total_k, cudaStream_t stream);
-// Same pipeline in persistent blocks that pull (sequence, query tile, head) items from a global
-// counter; batch <= 1024.
+// tcgen05 / TMEM / TMA kernel in persistent blocks that pull (sequence, query tile, head) items
+// from a global counter; batch <= kPrefillMaxBatch.  total_q / total_k bound the tiled loads.
 int launch_prefill_tcp(const PrefillParams& p, int64_t total_q, int64_t total_k, cudaStream_t stream);
 
 }  // namespace nvllm

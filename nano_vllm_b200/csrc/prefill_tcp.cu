@@ -1,10 +1,16 @@
-// Persistent variant of the tcgen05 prefill kernel (head_dim 64 or 128).
+// Varlen causal GQA prefill on the 5th-generation tensor cores (tcgen05 + TMEM + TMA), head_dim
+// 64 or 128.  Math follows the prefill branch of nanovllm/layers/attention.py:67-73
+// (flash_attn_varlen_func, causal, optional block table).
 //
-// Same tile pipeline as prefill_tc.cu (128 query rows x 64-key tiles, S double-buffered in
-// TMEM, P fed back from TMEM, two-stage K/V ring, one commit per MMA group), but a thread
-// block does not end with its query tile: two blocks per SM stay resident for the whole launch,
-// keep their TMEM allocation and barriers, and pull work items (sequence, query tile, head
-// group) from a global counter.  Under grouped-query attention the 128 rows of a tile are
+// Tile pipeline: 128 query rows x 64-key tiles; S = Q K^T (SS form, both operands K-major in
+// shared memory) into one of two S buffers in TMEM; the softmax warps (thread = query row) read
+// their row of S with tcgen05.ld, write P as packed bf16 over it with tcgen05.st; O += P V (TS
+// form: P from TMEM, V as an MN-major shared-memory operand); Q, K, V arrive by TMA tile loads
+// (128-byte swizzle, no multicast) into a two-stage ring; one tcgen05.commit per MMA group.
+// Six warps: 0-3 softmax / correction / epilogue, warp 4 lane 0 = TMA producer, warp 5 lane 0 =
+// MMA issuer.  A thread block does not end with its query tile: two blocks per SM stay resident
+// for the whole launch, keep their TMEM allocation and barriers, and pull work items (sequence,
+// query tile, head group) from a global counter.  Under grouped-query attention the 128 rows of a tile are
 // 128/n tokens x n query heads that share a KV head (n = 1, 2, 4 or 8), not 128 tokens of one
 // head: the causal diagonal and the ragged end of a sequence then cut through a narrower band
 // of tokens, so fewer of the issued products are masked or padding.  What this buys on short prompts, where a block only has a handful of
@@ -51,7 +57,7 @@ using namespace sm100;
 
 namespace tcp {
 using namespace tc;
-constexpr int MAX_BATCH = 1024;  // prefix array of query tiles per sequence lives in shared memory
+constexpr int MAX_BATCH = kPrefillMaxBatch;  // prefix array of query tiles per sequence lives in shared memory
 constexpr int SORT_BATCH = 256;  // batches up to this size are ranked by length (B^2 / 192 compares per thread)
 enum PBar {
   ITEM_FULL0 = tc::NUM_BARS, ITEM_FULL1, ITEM_FREE0, ITEM_FREE1, O_FREE, P_NUM_BARS

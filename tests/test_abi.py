@@ -113,3 +113,12 @@ def test_public_header_is_valid_c99_and_cxx():
                 ["g++", "-std=c++17", "-Wall", "-Werror", "-fsyntax-only", "-x", "c++", str(header)]):
         proc = subprocess.run(cmd, capture_output=True, text=True)
         assert proc.returncode == 0, proc.stderr
+
+
+def test_prefill_rejects_more_sequences_than_one_launch_holds(lib):
+    """Host-side check before any launch: the persistent kernel keeps its per-sequence tables in
+    shared memory, 1024 sequences at most (nano-vllm schedules 512 per step at most)."""
+    p16 = ctypes.c_void_p(4096)
+    rc = lib.nvllm_prefill_varlen(p16, 2048, p16, 1024, p16, 1024, None, 0, 0, p16, 2048, p16, p16, 4000, 4000, 1025, 100, 100,
+                                  16, 8, 128, ctypes.c_float(0.1), 0, None)
+    assert rc == -3 and "1024" in _lib.last_error()

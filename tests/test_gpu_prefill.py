@@ -86,11 +86,11 @@ def test_stale_cache_rows_past_the_sequence_cannot_leak(cuda, d):
     _check(cuda, case, f"stale d{d}")
 
 
-@pytest.mark.parametrize("impl,d", [("mma", 64), ("mma", 128), ("tc", 128), ("tcp", 64), ("tcp", 128)])
+@pytest.mark.parametrize("impl,d", [("mma", 64), ("mma", 128), ("tcp", 64), ("tcp", 128)])
 def test_every_prefill_kernel_on_the_same_case(cuda, monkeypatch, impl, d):
-    """NVLLM_PREFILL_IMPL selects the warp-level kernel (mma), the one-block-per-tile tcgen05
-    kernel (tc, head_dim 128 only) or the persistent tcgen05 kernel (tcp); all must agree with
-    the oracle on packed and on prefix-cached inputs."""
+    """NVLLM_PREFILL_IMPL=mma selects the warp-level cross-check kernel instead of the persistent
+    tcgen05 kernel (tcp, the default); both must agree with the oracle on packed and on
+    prefix-cached inputs."""
     monkeypatch.setenv("NVLLM_PREFILL_IMPL", impl)
     case = W.make_prefill_case(26, 7, 1, 1, 8, 2, d, lengths=[1, 130, 1024, 1024, 513, 700, 64],
                                shared_blocks=[0, 0, 0, 3, 0, 2, 0])

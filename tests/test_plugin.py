@@ -90,3 +90,49 @@ else:
     print("ok")
 """)
     assert out == "ok"
+
+
+def test_lm_head_step_sends_the_temperatures_to_the_worker_ranks():
+    """The sequences that reach a worker rank are pickled without sampling parameters
+    (nanovllm/engine/sequence.py:74-76); with the vocabulary-sharded sampling step every rank
+    samples, so rank 0's call("run", seqs, is_prefill) must carry the step's temperatures, and the
+    LM head must keep its slice of the logits instead of gathering."""
+    out = _run(PRELUDE + """
+from nano_vllm_b200 import plugin
+plugin.install()
+import torch, types
+import nanovllm.engine.model_runner as mr, nanovllm.layers.embed_head as eh
+from nanovllm.utils.context import set_context
+stock_forward, stock_call, stock_run = eh.ParallelLMHead.forward, mr.ModelRunner.call, mr.ModelRunner.run
+plugin.fuse_lm_head(seed=7)
+assert eh.ParallelLMHead.forward is not stock_forward and mr.ModelRunner.call is not stock_call
+assert mr.ModelRunner.run is not stock_run
+# rank 0 of two: the message to the workers and the local call both get the temperatures
+runner = object.__new__(mr.ModelRunner)
+runner.world_size, runner.rank = 2, 0
+sent, ran = [], []
+runner.write_shm = lambda name, *args: sent.append((name, args))
+runner.run = lambda *args: ran.append(args) or "tokens"
+seqs = [types.SimpleNamespace(temperature=0.0), types.SimpleNamespace(temperature=0.6)]
+assert runner.call("run", seqs, False) == "tokens"
+assert sent == [("run", (seqs, False, [0.0, 0.6]))] and ran == [(seqs, False, [0.0, 0.6])]
+# other methods and single-rank runs are passed through untouched
+runner.exit = lambda: "bye"
+assert runner.call("exit") == "bye" and sent[-1] == ("exit", ())
+runner.world_size = 1
+assert runner.call("run", seqs, True) == "tokens" and ran[-1] == (seqs, True)
+# the head keeps its slice: no gather, last rows only under prefill
+head = object.__new__(eh.ParallelLMHead)
+torch.nn.Module.__init__(head)
+head.tp_size, head.tp_rank = 2, 1
+head.weight = torch.nn.Parameter(torch.randn(6, 4))
+head.bias = None
+x = torch.randn(5, 4)
+set_context(True, cu_seqlens_q=torch.tensor([0, 2, 5], dtype=torch.int32))
+y = head(x)
+assert y.shape == (2, 6) and torch.allclose(y, x[[1, 4]] @ head.weight.T)
+set_context(False)
+assert head(x).shape == (5, 6)
+print("ok")
+""")
+    assert out == "ok"
