@@ -39,6 +39,15 @@ extern "C" int nvllm_prefill_varlen(const void* q, int64_t q_row_stride, const v
     if (k_row_stride % 8 || v_row_stride % 8)
       return fail(NVLLM_E_ALIGN, "prefill_varlen: k/v row strides must be multiples of 8 elements");
   }
+  // The persistent tcgen05 kernel is the product.  NVLLM_PREFILL_IMPL=mma (read on every call)
+  // selects the warp-level mma.sync kernel instead: the cross-check of the tests and the A/B
+  // baseline of measurements, never chosen by the library itself.
+  const char* forced = std::getenv("NVLLM_PREFILL_IMPL");
+  const bool has_rows = block_tables || total_k > 0;
+  const bool use_mma = (forced && forced[0] == 'm') || !has_rows;
+  if (!use_mma && batch > kPrefillMaxBatch)
+    return fail(NVLLM_E_GEOMETRY, "prefill_varlen: batch=%d exceeds the %d sequences of one launch", batch, kPrefillMaxBatch);
+  if (batch > 65535) return fail(NVLLM_E_GEOMETRY, "prefill_varlen: batch=%d outside the launch limits", batch);
   PrefillParams p;
   p.status = status_word();
   if (!p.status) return fail(NVLLM_E_NO_DEVICE, "prefill_varlen: no CUDA device is usable");
@@ -65,13 +74,6 @@ extern "C" int nvllm_prefill_varlen(const void* q, int64_t q_row_stride, const v
   p.pack = 1;
   p.scale_log2e = scale * 1.4426950408889634f;
   p.num_blocks = num_blocks;
-  // The persistent tcgen05 kernel is the product.  NVLLM_PREFILL_IMPL=mma (read on every call)
-  // selects the warp-level mma.sync kernel instead: the cross-check of the tests and the A/B
-  // baseline of measurements, never chosen by the library itself.
-  const char* forced = std::getenv("NVLLM_PREFILL_IMPL");
-  const bool has_rows = block_tables || total_k > 0;
-  if ((forced && forced[0] == 'm') || !has_rows) return launch_prefill_mma(p, static_cast<cudaStream_t>(stream));
-  if (batch > kPrefillMaxBatch)
-    return fail(NVLLM_E_GEOMETRY, "prefill_varlen: batch=%d exceeds the %d sequences of one launch", batch, kPrefillMaxBatch);
+  if (use_mma) return launch_prefill_mma(p, static_cast<cudaStream_t>(stream));
   return launch_prefill_tcp(p, total_q, total_k, static_cast<cudaStream_t>(stream));
 }
