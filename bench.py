@@ -75,8 +75,8 @@ def parse_args():
     ap.add_argument("--no-engine", action="store_true",
                     help="skip the end-to-end nano-vllm engine runs (output tok/s) that close the line")
     ap.add_argument("--kernel", default=None,
-                    choices=["prefill", "prefill_long", "prefill_d64", "store", "decode", "decode_tp8", "decode_long", "sampler",
-                             "allreduce"],
+                    choices=["prefill", "prefill_long", "prefill_d64", "store", "decode", "decode_tp8", "decode_engine",
+                             "decode_long", "sampler", "allreduce"],
                     help="time only this kernel and print its line (profiling aid; allreduce runs under torchrun)")
     ap.add_argument("--ar-protocol", type=int, default=0, choices=[0, 1, 2, 3],
                     help="with --kernel allreduce: force a protocol (0 automatic, 1 cells, 2 one shot, 3 two shots)")
@@ -586,6 +586,12 @@ def secondary(dev, hbm_peak_gbs, only=None, compare=None):
         c8 = W.cfg4_decode(8, 0, dev)
         decode_lines("decode_cfg4_b256_tp8_shard", c8, 20)
         del c8
+    if only == "decode_engine":
+        # what a decode step of the end-to-end workload looks like to one layer: Qwen3-0.6B heads, 256
+        # sequences of 100-2048 tokens, table as wide as max_model_len = 4096 allows
+        ce = W.make_decode_case(3, 256, 100, 2048, device=dev, table_width=16, **W.QWEN3_06B)
+        decode_lines("decode_qwen3_0.6b_b256_ctx100-2048", ce, 20)
+        del ce
     if only in (None, "sampler"):
         # the engine's decode-step tail: one token per row of [256, 151936] bf16 logits, T = 0.6
         lg = (torch.randn(256, 151936, device=dev) * 2).to(torch.bfloat16)
@@ -632,15 +638,20 @@ def _clean_env():
     return {k: v for k, v in os.environ.items() if k not in drop and not k.startswith("TORCHELASTIC_")}
 
 
-def _wait_for_free_gpus(n, seconds=30):
-    """The other ranks of the kernel benchmark exit on their own; wait until their memory is back."""
-    import torch
+def _wait_for_free_gpus(seconds=30):
+    """The other ranks of the kernel benchmark exit on their own; wait until no other compute
+    process is left on the visible GPUs (asked of nvidia-smi, so that this process opens no context
+    on the other ranks' devices)."""
     deadline = time.time() + seconds
+    me = str(os.getpid())
     while time.time() < deadline:
         try:
-            if all(torch.cuda.mem_get_info(i)[0] > 0.9 * torch.cuda.mem_get_info(i)[1] for i in range(1, n)):
-                return
+            out = subprocess.run(["nvidia-smi", "--query-compute-apps=pid", "--format=csv,noheader"],
+                                 capture_output=True, text=True, timeout=20).stdout.split()
         except Exception:
+            time.sleep(5)
+            return
+        if all(pid == me for pid in out):
             return
         time.sleep(0.5)
 
@@ -670,7 +681,7 @@ def engine_runs(tp):
     if not (ROOT / "baseline" / "_ref" / "nanovllm").is_dir():
         return {"unavailable": "no nano-vllm install under baseline/_ref"}
     if tp > 1:
-        _wait_for_free_gpus(tp)
+        _wait_for_free_gpus()
     mine = "b200-full-ar" if tp > 1 else "b200-full"
     plan = [("qwen3-0.6b", "b200", mine), ("qwen3-0.6b", "reference", "reference")]
     if tp > 1:
