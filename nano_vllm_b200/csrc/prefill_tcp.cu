@@ -34,23 +34,11 @@
 // 64-byte row segments.
 #include <atomic>
 #include <cstdlib>
-#include <type_traits>
 
 #include "common.cuh"
 #include "prefill.cuh"
 #include "prefill_tc.cuh"
 #include "sm100.cuh"
-
-// 1: an item's epilogue is carried into the next item's first key tile (see the softmax warps);
-// 0: it runs as soon as the item's last product is done (A/B builds).
-#ifndef NVLLM_PREFILL_CARRY
-#define NVLLM_PREFILL_CARRY 1
-#endif
-// 1: the S product of the next item's first key tile is issued before the current item's last
-// P V product; 0: after it (A/B builds).
-#ifndef NVLLM_PREFILL_LOOKAHEAD
-#define NVLLM_PREFILL_LOOKAHEAD 1
-#endif
 
 namespace nvllm {
 using namespace sm100;
@@ -325,37 +313,18 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
         umma_commit(bar(QK_DONE0 + st));
         return true;
       };
-      // The products form one stream over the block's key tiles, across items: S of tile t+1 is
-      // always issued before P V of tile t, so that it runs under tile t's softmax -- also when
-      // tile t+1 is the first tile of the NEXT item (its Q is loaded as soon as the current item's
-      // last S product has finished, well before the current item's last softmax ends).
       int T = 0, nq = 0;
       bool ok = true;
-      Item x;
-      x.n_kv = -1;
-      if ((ok = wait_or_abort(bar(ITEM_FULL0), 0, abort_flag))) x = read_item(0);
-      if (ok && x.n_kv > 0) {
-        if ((ok = wait_or_abort(bar(Q_FULL), nq & 1, abort_flag))) {
-          ++nq;
-          ok = issue_qk(T);
-        }
-      }
-      for (int it = 0; ok && x.n_kv > 0; ++it) {
-        Item nx;
-        nx.n_kv = -1;
+      for (int it = 0; ok; ++it) {
+        if (!(ok = wait_or_abort(bar(ITEM_FULL0 + (it & 1)), (it >> 1) & 1, abort_flag))) break;
+        const Item x = read_item(it);
+        if (x.n_kv < 0) break;
+        if (!(ok = wait_or_abort(bar(Q_FULL), nq & 1, abort_flag))) break;
+        ++nq;
+        if (!(ok = issue_qk(T))) break;
         for (int j = 0; j < x.n_kv; ++j) {
           const int t = T + j, st = t & 1, ph = (t >> 1) & 1;
-          if (j + 1 < x.n_kv) {
-            if (!(ok = issue_qk(t + 1))) break;  // next S runs under this tile's softmax
-          } else if (NVLLM_PREFILL_LOOKAHEAD) {
-            if (!(ok = wait_or_abort(bar(ITEM_FULL0 + ((it + 1) & 1)), ((it + 1) >> 1) & 1, abort_flag))) break;
-            nx = read_item(it + 1);
-            if (nx.n_kv > 0) {
-              if (!(ok = wait_or_abort(bar(Q_FULL), nq & 1, abort_flag))) break;
-              ++nq;
-              if (!(ok = issue_qk(t + 1))) break;  // the next item's first S
-            }
-          }
+          if (j + 1 < x.n_kv && !(ok = issue_qk(t + 1))) break;  // next S runs under this tile's softmax
           if (!(ok = wait_or_abort(bar(V_FULL0 + st), ph, abort_flag))) break;
           if (!(ok = wait_or_abort(bar(P_FULL0 + st), ph, abort_flag))) break;
           // the first product of an item overwrites O: the previous item's O must have been read
@@ -372,16 +341,6 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
         if (!ok) break;
         T += x.n_kv;
         mbar_arrive(bar(ITEM_FREE0 + (it & 1)));
-        if (!NVLLM_PREFILL_LOOKAHEAD) {
-          if (!(ok = wait_or_abort(bar(ITEM_FULL0 + ((it + 1) & 1)), ((it + 1) >> 1) & 1, abort_flag))) break;
-          nx = read_item(it + 1);
-          if (nx.n_kv > 0) {
-            if (!(ok = wait_or_abort(bar(Q_FULL), nq & 1, abort_flag))) break;
-            ++nq;
-            if (!(ok = issue_qk(T))) break;
-          }
-        }
-        x = nx;
       }
       if (!ok) {  // make sure nothing is still running on TMEM before it is freed
         umma_commit(bar(DRAIN));
@@ -407,26 +366,20 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
       st_toks |= static_cast<uint32_t>(tok) << (8 * i);
       st_off[i] = tok * static_cast<int>(p.out_stride) + (row - tok * pack) * D + spiece * 8;
     }
-    // The epilogue of an item (O / l -> bf16 rows in the output) does not run when the item's last
-    // product is done: it is carried into the first key tile of the NEXT item and done there 32
-    // columns at a time between the stages of that tile's softmax, so that the TMEM loads, the
-    // pass through shared memory and the global stores fill the softmax's latency gaps instead of
-    // standing in front of it.  O is free for the next item's first product well before that
-    // tile's P is ready.  Only the block's last item has its epilogue on its own.
-    bool pend = false;
-    float pend_inv = 0.f;
-    __nv_bfloat16* pend_out = nullptr;
-    int pend_toks = 0, pend_t = 0;
+    // the item whose epilogue is running
+    float epi_inv = 0.f;
+    __nv_bfloat16* epi_out = nullptr;
+    int epi_toks = 0;
     // 32 columns of O (already in `o`) -> output rows; then starts the load of the next 32, or,
     // after the last, releases O.
     auto epilogue_chunk = [&](int c, uint32_t (&o)[32]) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         uint4 v;
-        v.x = pack_bf16x2(__uint_as_float(o[8 * k]) * pend_inv, __uint_as_float(o[8 * k + 1]) * pend_inv);
-        v.y = pack_bf16x2(__uint_as_float(o[8 * k + 2]) * pend_inv, __uint_as_float(o[8 * k + 3]) * pend_inv);
-        v.z = pack_bf16x2(__uint_as_float(o[8 * k + 4]) * pend_inv, __uint_as_float(o[8 * k + 5]) * pend_inv);
-        v.w = pack_bf16x2(__uint_as_float(o[8 * k + 6]) * pend_inv, __uint_as_float(o[8 * k + 7]) * pend_inv);
+        v.x = pack_bf16x2(__uint_as_float(o[8 * k]) * epi_inv, __uint_as_float(o[8 * k + 1]) * epi_inv);
+        v.y = pack_bf16x2(__uint_as_float(o[8 * k + 2]) * epi_inv, __uint_as_float(o[8 * k + 3]) * epi_inv);
+        v.z = pack_bf16x2(__uint_as_float(o[8 * k + 4]) * epi_inv, __uint_as_float(o[8 * k + 5]) * epi_inv);
+        v.w = pack_bf16x2(__uint_as_float(o[8 * k + 6]) * epi_inv, __uint_as_float(o[8 * k + 7]) * epi_inv);
         *reinterpret_cast<uint4*>(stage + lane * 64 + ((k ^ ((lane >> 1) & 3)) << 4)) = v;
       }
       if (c + 1 < OCH) {
@@ -441,34 +394,15 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
       for (int i = 0; i < 4; ++i) {
         const int lr = i * 8 + srow;  // row within the warp's 32
         const uint4 v = *reinterpret_cast<const uint4*>(stage + lr * 64 + ((spiece ^ ((lr >> 1) & 3)) << 4));
-        if (static_cast<int>((st_toks >> (8 * i)) & 0xffu) < pend_toks) *reinterpret_cast<uint4*>(pend_out + st_off[i] + c * 32) = v;
+        if (static_cast<int>((st_toks >> (8 * i)) & 0xffu) < epi_toks) *reinterpret_cast<uint4*>(epi_out + st_off[i] + c * 32) = v;
       }
       __syncwarp();
     };
     int T = 0;
     bool ok = true;
     PROF_DECL;
-    // The pending epilogue on its own (the block's last item).
-    auto epilogue_now = [&]() -> bool {
-      if (!wait_or_abort(bar(PV_DONE0 + (pend_t & 1)), (pend_t >> 1) & 1, abort_flag)) return false;
-      PROF(4);
-      tc_fence_after();
-      uint32_t ob[32];
-      tmem_ld32(tmem_o + lane_addr, ob);
-#pragma unroll
-      for (int c = 0; c < OCH; ++c) {
-        tmem_wait_ld();
-        epilogue_chunk(c, ob);
-      }
-      PROF(5);
-      pend = false;
-      return true;
-    };
-    // One key tile of an item: scores -> P.  Two compiled variants: the plain one, and the one for
-    // an item's first tile that also carries the previous item's epilogue (kept apart so that the
-    // plain tile does not pay for the epilogue's registers).  Returns false when a wait gave up.
-    auto do_tile = [&](auto carries_epilogue, const Item& x, int j, float& m_used, float& l) -> bool {
-      constexpr bool EPI = decltype(carries_epilogue)::value;
+    // One key tile of an item: scores -> P.  Returns false when a wait gave up.
+    auto do_tile = [&](const Item& x, int j, float& m_used, float& l) -> bool {
       const int qi = x.m0 + r_tok, off = x.Lk - x.Lq;
       const int t = T + j, st = t & 1, ph = (t >> 1) & 1;
       const uint32_t tmem_s = tmem + st * 64 + lane_addr;
@@ -479,15 +413,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
       uint32_t s[64];
       tmem_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
       tmem_ld32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-      uint32_t ob[EPI ? 32 : 1];
-      if constexpr (EPI) {
-        if (!wait_or_abort(bar(PV_DONE0 + (pend_t & 1)), (pend_t >> 1) & 1, abort_flag)) return false;
-        PROF(4);  // waiting for the previous item's last product
-        tc_fence_after();
-        tmem_ld32(tmem_o + lane_addr, ob);
-      }
       tmem_wait_ld();
-      if constexpr (EPI) epilogue_chunk(0, ob);
 
       const int j0 = j * BN;
       if ((j0 + BN - 1 > x.m0 + off) || (j0 + BN > x.Lk)) {  // tile touches the diagonal or the end
@@ -515,57 +441,34 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
           m_used = m_new;
           l *= alpha;
         }
-        if constexpr (!EPI) {
-          if (j > 0) {  // O holds tiles 0..j-1 of this item once the previous P V product has finished
-            PROF(2);
-            if (!wait_or_abort(bar(PV_DONE0 + ((t - 1) & 1)), ((t - 1) >> 1) & 1, abort_flag)) return false;
-            PROF(3);  // waiting for O before a rescale
-            tc_fence_after();
+        if (j > 0) {  // O holds tiles 0..j-1 of this item once the previous P V product has finished
+          PROF(2);
+          if (!wait_or_abort(bar(PV_DONE0 + ((t - 1) & 1)), ((t - 1) >> 1) & 1, abort_flag)) return false;
+          PROF(3);  // waiting for O before a rescale
+          tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < OCH; ++c) {
-              uint32_t o[32];
-              tmem_ld32(tmem_o + lane_addr + c * 32, o);
-              tmem_wait_ld();
+          for (int c = 0; c < OCH; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tmem_o + lane_addr + c * 32, o);
+            tmem_wait_ld();
 #pragma unroll
-              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-              tmem_st32(tmem_o + lane_addr + c * 32, o);
-            }
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st32(tmem_o + lane_addr + c * 32, o);
           }
         }
-      }
-      if constexpr (EPI && OCH > 1) {
-        tmem_wait_ld();
-        epilogue_chunk(1, ob);
       }
       const float msub = (m_used == -INFINITY) ? 0.f : m_used;
       // p = 2^(s * scale - m): the multiply-subtract and the row sum run two lanes at a time
       const uint64_t scale2 = pack2(p.scale_log2e, p.scale_log2e), nmsub2 = pack2(-msub, -msub);
       uint64_t sum2[2] = {0ull, 0ull};
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {  // P is packed in place: s[c] <- (p[2c], p[2c+1])
+      for (int c = 0; c < 32; ++c) {  // P is packed in place: s[c] <- (p[2c], p[2c+1])
         float a0, a1;
         unpack2(fma2(pack2(__uint_as_float(s[2 * c]), __uint_as_float(s[2 * c + 1])), scale2, nmsub2), a0, a1);
         const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
         sum2[c & 1] = add2(sum2[c & 1], pack2(p0, p1));
         s[c] = pack_bf16x2(p0, p1);
       }
-      if constexpr (EPI && OCH > 2) {
-        tmem_wait_ld();
-        epilogue_chunk(2, ob);
-      }
-#pragma unroll
-      for (int c = 16; c < 32; ++c) {
-        float a0, a1;
-        unpack2(fma2(pack2(__uint_as_float(s[2 * c]), __uint_as_float(s[2 * c + 1])), scale2, nmsub2), a0, a1);
-        const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
-        sum2[c & 1] = add2(sum2[c & 1], pack2(p0, p1));
-        s[c] = pack_bf16x2(p0, p1);
-      }
-      if constexpr (EPI && OCH > 3) {
-        tmem_wait_ld();
-        epilogue_chunk(3, ob);
-      }
-      if constexpr (EPI) PROF(5);  // (softmax of this tile and) the previous item's epilogue
       {
         float t0, t1, t2, t3;
         unpack2(sum2[0], t0, t1);
@@ -600,26 +503,28 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
       if (x.n_kv < 0) break;
       PROF_COUNT(6);
       float m_used = -INFINITY, l = 0.f;
-      int j = 0;
-      if (NVLLM_PREFILL_CARRY && pend) {  // warp-uniform: the previous item's epilogue rides on this item's first tile
-        if (!(ok = do_tile(std::true_type{}, x, 0, m_used, l))) break;
-        pend = false;
-        j = 1;
-      }
-      for (; j < x.n_kv; ++j)
-        if (!(ok = do_tile(std::false_type{}, x, j, m_used, l))) break;
+      for (int j = 0; j < x.n_kv; ++j)
+        if (!(ok = do_tile(x, j, m_used, l))) break;
       if (!ok) break;
       T += x.n_kv;
-      // this item's epilogue: during the next item's first tile (or after the loop if none follows)
-      pend = true;
-      pend_inv = l > 0.f ? 1.f / l : 0.f;
-      pend_out = p.out + static_cast<int64_t>(x.q0 + x.m0) * p.out_stride + x.h * D;
-      pend_toks = min(BMT, x.Lq - x.m0);
-      pend_t = T - 1;
-      if (lane == 0) mbar_arrive(bar(ITEM_FREE0 + (it & 1)));  // the item's descriptor is in registers
-      if (!NVLLM_PREFILL_CARRY && !(ok = epilogue_now())) break;
+
+      // epilogue: O / l -> bf16; 32 columns at a time through this warp's patch of shared memory
+      if (!(ok = wait_or_abort(bar(PV_DONE0 + ((T - 1) & 1)), ((T - 1) >> 1) & 1, abort_flag))) break;
+      PROF(4);  // waiting for the last product before the epilogue
+      tc_fence_after();
+      epi_inv = l > 0.f ? 1.f / l : 0.f;
+      epi_out = p.out + static_cast<int64_t>(x.q0 + x.m0) * p.out_stride + x.h * D;
+      epi_toks = min(BMT, x.Lq - x.m0);
+      uint32_t ob[32];
+      tmem_ld32(tmem_o + lane_addr, ob);
+#pragma unroll
+      for (int c = 0; c < OCH; ++c) {
+        tmem_wait_ld();
+        epilogue_chunk(c, ob);  // starts the load of the next 32 columns; releases O after the last
+      }
+      if (lane == 0) mbar_arrive(bar(ITEM_FREE0 + (it & 1)));
+      PROF(5);  // epilogue
     }
-    if (ok && pend) ok = epilogue_now();  // the block's last item
 #ifdef NVLLM_PREFILL_PROFILE
     if (tid == 0 && blockIdx.x < 2048)
       for (int i = 0; i < 8; ++i) g_prefill_prof[blockIdx.x * 8 + i] = prof[i];
