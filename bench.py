@@ -78,8 +78,9 @@ def parse_args():
                     choices=["prefill", "prefill_long", "prefill_d64", "store", "decode", "decode_tp8", "decode_engine",
                              "decode_long", "sampler", "allreduce"],
                     help="time only this kernel and print its line (profiling aid; allreduce runs under torchrun)")
-    ap.add_argument("--ar-protocol", type=int, default=0, choices=[0, 1, 2, 3],
-                    help="with --kernel allreduce: force a protocol (0 automatic, 1 cells, 2 one shot, 3 two shots)")
+    ap.add_argument("--ar-protocol", type=int, default=0, choices=[0, 1, 2, 3, 4],
+                    help="with --kernel allreduce: force a protocol (0 automatic, 1 cells, 2 one shot, 3 two shots, "
+                         "4 cells in two shots)")
     ap.add_argument("--with-flash-attn", action="store_true",
                     help="with --kernel: also time the library kernels the reference calls (flash-attn, Triton "
                          "store) on the same inputs, if they are importable")
@@ -746,7 +747,7 @@ def run_allreduce(args):
 
     ar = PeerAllReduce(rank, world, 8 << 20, wait_ms=20000)
     ar.force_protocol(args.ar_protocol)
-    for rows, hidden in ((16, 1024), (256, 1024), (64, 4096), (256, 4096), (512, 4096)):
+    for rows, hidden in ((16, 1024), (64, 1024), (256, 1024), (128, 4096), (256, 4096), (512, 4096)):
         x = (torch.randn(rows, hidden, generator=torch.Generator().manual_seed(rank)) * 0.5).to(torch.bfloat16).cuda()
         y1, y2 = x.clone(), x.clone()
         ar.all_reduce(y1)

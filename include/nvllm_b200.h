@@ -293,7 +293,7 @@ NVLLM_API int nvllm_decode_step_inputs(const void* staged, int64_t tokens_off, i
  * GPU.  Replaces dist.all_reduce in RowParallelLinear.forward (nanovllm/layers/linear.py:195-199)
  * for tensors up to `max_bytes`.  Set-up, once per process and device, outside stream capture:
  *   nvllm_ar_init(rank, world, max_bytes, handle_out)  allocates this rank's flag + staging area
- *       (8 KB + 6 * max_bytes of device memory) and writes its CUDA IPC handle
+ *       (8 KB + 8 * max_bytes of device memory) and writes its CUDA IPC handle
  *       (nvllm_ar_handle_bytes() bytes) to handle_out;
  *   the caller gathers the handles of all ranks (rank order) by its own means;
  *   nvllm_ar_connect(all_handles)  maps every peer's area.
@@ -302,13 +302,14 @@ NVLLM_API int nvllm_decode_step_inputs(const void* staged, int64_t tokens_off, i
  * other (one stream, or otherwise serialised: the staging buffers belong to one call at a
  * time).  in == out is allowed; both 16-byte aligned;
  * n_elems * 2 <= max_bytes.  All ranks get bit-identical sums (fp32 accumulation in rank order).
- * The call picks one of three protocols from (n_elems, world, max_bytes) alone, the same on every
- * rank: flagged 16-byte cells pushed to every peer (small tensors: one NVLink crossing of
- * latency), staging + flags with every rank pulling all peers' tensors (one shot), or, at more
- * than two ranks, reduce-scatter + all-gather over pushed slices (two shots: a rank moves
- * 2 (world-1)/world of the tensor instead of world-1 of it).  nvllm_ar_protocol() reports the
- * choice (1 cells, 2 one shot, 3 two shots); nvllm_ar_set_protocol() forces one where it applies
- * (0 = automatic; measurement aid; every rank must set the same).
+ * The call picks one of four protocols from (n_elems, world, max_bytes) alone, the same on every
+ * rank: (1) flagged 16-byte cells pushed to every peer (small tensors: one NVLink crossing of
+ * latency, twice the bytes on the wire); (4) flagged cells in two shots at more than two ranks (a
+ * rank sends the cells of slice j to its owner j only, the owner sums and sends the result cells to
+ * everyone); (2) staging + flags with every rank pulling all peers' tensors (one shot); (3)
+ * staging + flags in two shots (pushed reduce-scatter + all-gather).  nvllm_ar_protocol() reports
+ * the choice; nvllm_ar_set_protocol() forces one where it applies (0 = automatic; measurement aid;
+ * every rank must set the same).
  * No allocation, synchronisation or host read in the call: legal during stream capture, and a
  * captured graph can be replayed (call counts live in device memory).  A peer that does not
  * arrive within ~1 s of SM clocks sets NVLLM_STATUS_TIMEOUT; that call's output is invalid and

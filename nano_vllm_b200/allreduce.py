@@ -25,7 +25,7 @@ def gather_handles(handle: bytes, rank: int, world: int, dist=None) -> bytes:
     return b"".join(parts)
 
 
-PROTOCOLS = {0: "auto", 1: "cells", 2: "one-shot", 3: "two-shot"}
+PROTOCOLS = {0: "auto", 1: "cells", 2: "one-shot", 3: "two-shot", 4: "cells-two-shot"}
 
 
 def protocol_for(nbytes: int, world: int, max_bytes: int, forced: int = 0) -> str:
@@ -71,7 +71,7 @@ class PeerAllReduce:
         return protocol_for(nbytes, self.world, self.max_bytes, self.forced)
 
     def force_protocol(self, protocol: int) -> None:
-        """0 automatic, 1 cells, 2 one shot, 3 two shots; every rank must set the same."""
+        """0 automatic, 1 cells, 2 one shot, 3 two shots, 4 cells in two shots; every rank must set the same."""
         _lib.check(_lib.load().nvllm_ar_set_protocol(protocol))
         self.forced = protocol
 
@@ -92,7 +92,7 @@ def all_reduce_emulated(inputs: list[torch.Tensor], scratch: torch.Tensor, max_b
                         absent_rank: int = -1, protocol: int = 0) -> list[torch.Tensor]:
     """All ranks' reductions in one cooperative launch on one device (test aid): returns one
     output per rank.  ``scratch``: uint8, zero-filled before its first use, kept between calls.
-    ``protocol``: 0 automatic, 1 cells, 2 one shot, 3 two shots."""
+    ``protocol``: 0 automatic, 1 cells, 2 one shot, 3 two shots, 4 cells in two shots."""
     world = len(inputs)
     outs = [torch.empty_like(x) for x in inputs]
     arr = ctypes.c_void_p * world

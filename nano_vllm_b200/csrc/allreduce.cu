@@ -7,9 +7,9 @@
 // allocation that all its peers map through CUDA IPC:
 //
 //     [ flags: kMaxBlocks x kMaxRanks u32 | call counts | staging 0 | staging 1 | cells 0 | cells 1 |
-//       result 0 | result 1 ]
+//       result 0 | result 1 | result cells 0 | result cells 1 ]
 //
-// Three protocols, chosen by size and world (the same choice on every rank).
+// Four protocols, chosen by size and world (the same choice on every rank).
 //
 // SMALL tensors (2 x bytes x world <= max_bytes): flagged cells, in the manner of NCCL's
 // low-latency protocol.  A cell is 16 bytes: 8 bytes of data and the call count twice
@@ -18,6 +18,12 @@
 // cell area of every peer (region [buffer][source rank]), then polls its OWN area (local memory)
 // until the cells of every peer carry this call's count, and sums in rank order.  No fence, no
 // separate flag round trip, no block-wide barrier: one NVLink crossing of latency.
+//
+// MEDIUM tensors at more than two ranks: flagged cells in two shots.  Pushing every cell to every
+// peer costs 2 x bytes x (world-1) on the wire; here the tensor is cut into `world` slices, a rank
+// pushes the cells of slice j to its owner j only, the owner sums them as they arrive and pushes
+// the cells of the result to every peer: 4 x bytes x (world-1)/world per rank, two NVLink
+// crossings of latency, still no fence, no flag round trip and no block-wide barrier.
 //
 // LARGER tensors, one shot: staging + flags.
 //
@@ -66,8 +72,8 @@ constexpr int64_t kBrokenOff = kEpochOff + kMaxBlocks * 4;     // u32 latch
 constexpr int64_t kCellEpochOff = kBrokenOff + 64;             // u32[kMaxBlocks], call counts of the cell protocol
 constexpr int64_t kHeaderBytes = 8192;
 static_assert(kCellEpochOff + kMaxBlocks * 4 <= kHeaderBytes, "header");
-constexpr int kAreas = 6;  // staging 0/1, cells 0/1, result 0/1: max_bytes each
-enum Protocol { kAuto = 0, kCells = 1, kOneShot = 2, kTwoShot = 3 };
+constexpr int kAreas = 8;  // staging 0/1, cells 0/1, result 0/1, result cells 0/1: max_bytes each
+enum Protocol { kAuto = 0, kCells = 1, kOneShot = 2, kTwoShot = 3, kCellsTwoShot = 4 };
 // Above this size the flagged cells (twice the bytes on the wire, to every peer) lose against two
 // shots at more than two ranks.
 constexpr int64_t kCellsMaxBytesManyRanks = 128 << 10;
@@ -279,6 +285,124 @@ __device__ void allreduce_cells_block(const Params& p, int rank, int b, int nblo
   if (tid == 0) epochs[b] = e;
 }
 
+// Flagged cells in two shots: the work of block `b` on behalf of rank `rank`.
+__device__ void allreduce_cells_twoshot_block(const Params& p, int rank, int b, int nblocks) {
+  __shared__ uint32_t s_epoch;
+  __shared__ int s_abort;
+  const int tid = threadIdx.x;
+  const int w = p.world;
+  unsigned char* own = p.peers.base[rank];
+  uint32_t* epochs = reinterpret_cast<uint32_t*>(own + kCellEpochOff);
+  uint32_t* broken = reinterpret_cast<uint32_t*>(own + kBrokenOff);
+  if (tid == 0) {
+    s_epoch = epochs[b] + 1;
+    s_abort = *reinterpret_cast<volatile uint32_t*>(broken) != 0;
+  }
+  __syncthreads();
+  const uint32_t e = s_epoch;
+  const int64_t n_elems = p.n16 * 8 + p.tail_elems;
+  const int64_t n_cells = (n_elems + 3) / 4;
+  const int64_t cells_cap = p.stage_bytes / 16 / w;  // cells per source rank in a first-shot area
+  const int64_t area1 = kHeaderBytes + (2 + static_cast<int64_t>(e & 1)) * p.stage_bytes;  // [source][cell of my slice]
+  const int64_t area2 = kHeaderBytes + (6 + static_cast<int64_t>(e & 1)) * p.stage_bytes;  // [cell of the tensor]
+  const uint2* in2 = reinterpret_cast<const uint2*>(p.in);
+  uint2* out2 = reinterpret_cast<uint2*>(p.out);
+  const __nv_bfloat16* in_e = reinterpret_cast<const __nv_bfloat16*>(p.in);
+  __nv_bfloat16* out_e = reinterpret_cast<__nv_bfloat16*>(p.out);
+  auto load_own = [&](int64_t c) {
+    if (4 * c + 4 <= n_elems) return in2[c];
+    __nv_bfloat16 t[4];  // the ragged last cell: missing elements are zero
+    for (int k = 0; k < 4; ++k) t[k] = 4 * c + k < n_elems ? in_e[4 * c + k] : __float2bfloat16(0.f);
+    return *reinterpret_cast<const uint2*>(t);
+  };
+  auto store_out = [&](int64_t c, const uint2& o) {
+    if (4 * c + 4 <= n_elems) {
+      out2[c] = o;
+    } else {
+      const __nv_bfloat16* t = reinterpret_cast<const __nv_bfloat16*>(&o);
+      for (int k = 0; k < 4; ++k)
+        if (4 * c + k < n_elems) out_e[4 * c + k] = t[k];
+    }
+  };
+  // this block's part [lo, hi) of slice j (slices and parts in cells)
+  auto part = [&](int j, int64_t& s0, int64_t& lo, int64_t& hi) {
+    s0 = n_cells * j / w;
+    const int64_t len = n_cells * (j + 1) / w - s0;
+    lo = s0 + len * b / nblocks;
+    hi = s0 + len * (b + 1) / nblocks;
+  };
+  bool gave_up = s_abort;
+  // a cell of this call, or (after the clock limit) whatever is there
+  auto wait_cell = [&](const uint4* src) {
+    uint4 v = ld_volatile16(src);
+    if (!gave_up && (v.y != e || v.w != e)) {
+      const long long t0 = clock64();
+      do {
+        v = ld_volatile16(src);
+        if (clock64() - t0 > p.wait_cycles) {
+          atomicOr(p.status, NVLLM_STATUS_TIMEOUT);
+          *reinterpret_cast<volatile uint32_t*>(broken) = 1;
+          gave_up = true;
+          break;
+        }
+      } while (v.y != e || v.w != e);
+    }
+    return v;
+  };
+
+  // 1. my cells of every other slice go to the slice's owner, region [source = rank]
+  for (int k = 1; k < w; ++k) {
+    const int j = (rank + k) % w;
+    int64_t s0, lo, hi;
+    part(j, s0, lo, hi);
+    uint4* dst = reinterpret_cast<uint4*>(p.peers.base[j] + area1) + rank * cells_cap - s0;
+    for (int64_t c = lo + tid; c < hi; c += blockDim.x) {
+      const uint2 d = load_own(c);
+      st_volatile16(dst + c, make_uint4(d.x, e, d.y, e));
+    }
+  }
+  // 2. my slice: sum in rank order as the peers' cells arrive; result to `out` and to every peer
+  {
+    int64_t s0, lo, hi;
+    part(rank, s0, lo, hi);
+    const uint4* mine = reinterpret_cast<const uint4*>(own + area1);
+    for (int64_t c = lo + tid; c < hi; c += blockDim.x) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < w; ++r) {
+        if (r == rank) {
+          const uint2 d = load_own(c);
+          add4(acc, d.x, d.y);
+        } else {
+          const uint4 v = wait_cell(mine + r * cells_cap + (c - s0));
+          add4(acc, v.x, v.z);
+        }
+      }
+      uint2 o;
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      store_out(c, o);
+      const uint4 cell = make_uint4(o.x, e, o.y, e);
+      for (int k = 1; k < w; ++k) {
+        const int j = (rank + k) % w;
+        st_volatile16(reinterpret_cast<uint4*>(p.peers.base[j] + area2) + c, cell);
+      }
+    }
+  }
+  // 3. the other slices' results arrive in my result-cell area
+  const uint4* results = reinterpret_cast<const uint4*>(own + area2);
+  for (int k = 1; k < w; ++k) {
+    const int j = (rank + k) % w;
+    int64_t s0, lo, hi;
+    part(j, s0, lo, hi);
+    for (int64_t c = lo + tid; c < hi; c += blockDim.x) {
+      const uint4 v = wait_cell(results + c);
+      store_out(c, make_uint2(v.x, v.z));
+    }
+  }
+  __syncthreads();
+  if (tid == 0) epochs[b] = e;
+}
+
 // Two shots: the work of block `b` (of `nblocks`) on behalf of rank `rank`.  tail_elems == 0.
 __device__ void allreduce_twoshot_block(const Params& p, int rank, int b, int nblocks) {
   __shared__ uint32_t s_epoch;
@@ -375,10 +499,14 @@ __host__ __device__ inline int pick_protocol(int64_t n16, int64_t tail_elems, in
   const int64_t n_elems = n16 * 8 + tail_elems;
   const bool cells_fit = 2 * ((n_elems + 3) / 4 * 8) * world <= stage_bytes;
   const bool twoshot_fits = world > 2 && tail_elems == 0 && (n16 + world - 1) / world <= stage_bytes / 16 / world;
+  const int64_t n_cells = (n_elems + 3) / 4;
+  const bool cells_twoshot_fits = world > 2 && (n_cells + world - 1) / world <= stage_bytes / 16 / world && n_cells * 16 <= stage_bytes;
   if (force == kCells && cells_fit) return kCells;
+  if (force == kCellsTwoShot && cells_twoshot_fits) return kCellsTwoShot;
   if (force == kTwoShot && twoshot_fits) return kTwoShot;
   if (force == kOneShot) return kOneShot;
   if (cells_fit && (world == 2 || n_elems * 2 <= kCellsMaxBytesManyRanks)) return kCells;
+  if (cells_twoshot_fits) return kCellsTwoShot;
   if (twoshot_fits) return kTwoShot;
   return kOneShot;
 }
@@ -386,6 +514,7 @@ __host__ __device__ inline int pick_protocol(int64_t n16, int64_t tail_elems, in
 __device__ __forceinline__ void allreduce_dispatch(const Params& p, int rank, int b, int nblocks) {
   const int proto = pick_protocol(p.n16, p.tail_elems, p.stage_bytes, p.world, p.force);
   if (proto == kCells) allreduce_cells_block(p, rank, b, nblocks);
+  else if (proto == kCellsTwoShot) allreduce_cells_twoshot_block(p, rank, b, nblocks);
   else if (proto == kTwoShot) allreduce_twoshot_block(p, rank, b, nblocks);
   else allreduce_block(p, rank, b, nblocks);
 }
@@ -437,7 +566,7 @@ static State* current_state() {
 // lock-step, so all blocks of a call use the same staging buffer and the two-buffer argument
 // above holds for the whole tensor (a block whose slice is empty still takes part in the
 // hand-shake).
-constexpr int kGrid = 64;
+constexpr int kGrid = 128;
 constexpr int kEmulatedGrid = 16;  // x ranks blocks must be resident together on one device
 static_assert(kGrid <= kMaxBlocks, "flag slots");
 
@@ -524,7 +653,7 @@ extern "C" int nvllm_ar_set_wait_ms(int64_t ms) {
 extern "C" int nvllm_ar_set_protocol(int32_t protocol) {
   ar::State* s = ar::current_state();
   if (!s || !s->ready) return fail(NVLLM_E_GEOMETRY, "ar_set_protocol: nvllm_ar_init has not run on this device");
-  if (protocol < ar::kAuto || protocol > ar::kTwoShot) return fail(NVLLM_E_GEOMETRY, "ar_set_protocol: %d is not 0..3", protocol);
+  if (protocol < ar::kAuto || protocol > ar::kCellsTwoShot) return fail(NVLLM_E_GEOMETRY, "ar_set_protocol: %d is not 0..4", protocol);
   s->force = protocol;
   return NVLLM_OK;
 }
@@ -576,7 +705,7 @@ extern "C" int nvllm_ar_allreduce_emulated(int32_t world, const void* const* inp
                                            void* scratch, int64_t scratch_bytes, int64_t max_bytes, int32_t absent_rank,
                                            int32_t protocol, void* stream) {
   if (world < 2 || world > ar::kMaxRanks) return fail(NVLLM_E_GEOMETRY, "ar_allreduce_emulated: world=%d invalid", world);
-  if (protocol < ar::kAuto || protocol > ar::kTwoShot) return fail(NVLLM_E_GEOMETRY, "ar_allreduce_emulated: protocol=%d invalid", protocol);
+  if (protocol < ar::kAuto || protocol > ar::kCellsTwoShot) return fail(NVLLM_E_GEOMETRY, "ar_allreduce_emulated: protocol=%d invalid", protocol);
   if (!inputs || !outputs || !scratch) return fail(NVLLM_E_NULL, "ar_allreduce_emulated: NULL pointer argument");
   if (max_bytes <= 0 || max_bytes % 16 || n_elems <= 0 || (n_elems * 2 + 15) / 16 * 16 > max_bytes)
     return fail(NVLLM_E_GEOMETRY, "ar_allreduce_emulated: sizes invalid");

@@ -40,13 +40,13 @@ def test_emulated_ranks_sum_bit_exactly_call_after_call(cuda, world):
 
 @pytest.mark.parametrize("world", [4, 8])
 def test_emulated_protocols_interleave(cuda, world):
-    """Cells, one shot and two shots in turn on one area (they share flags, call counts and
-    staging buffers), decode-step sizes; every rank must hold the oracle's sum bit for bit."""
+    """The four protocols in turn on one area (they share flags, call counts and buffers),
+    decode-step sizes and ragged ones; every rank must hold the oracle's sum bit for bit."""
     scratch = _scratch(cuda, world)
     g = torch.Generator().manual_seed(10 + world)
-    sizes = [256 * 1024, 16 * 1024, 64 * 4096, 256 * 4096, 8 * world, 1000 * 8, 256 * 1024]
-    for i, n in enumerate(sizes * 2):
-        proto = (3, 2, 1, 0)[i % 4]
+    sizes = [256 * 1024, 16 * 1024, 64 * 4096, 256 * 4096, 8 * world, 1000 * 8 + 3, 256 * 1024, 5]
+    for i, n in enumerate(sizes * 2 + sizes[:3]):
+        proto = (3, 4, 2, 1, 0)[i % 5]
         xs = [(torch.randn(n, generator=g) * 2).to(torch.bfloat16) for _ in range(world)]
         outs = AR.all_reduce_emulated([x.to(cuda) for x in xs], scratch, MAX_BYTES, protocol=proto)
         torch.cuda.synchronize()
@@ -56,13 +56,14 @@ def test_emulated_protocols_interleave(cuda, world):
     assert _lib.read_status() == 0
 
 
-def test_absent_peer_in_the_two_shot_protocol(cuda):
-    """Rank 2 of 4 never arrives: both hand-shakes of the other ranks run out, nothing hangs."""
+@pytest.mark.parametrize("protocol", [3, 4])
+def test_absent_peer_in_the_two_shot_protocols(cuda, protocol):
+    """Rank 2 of 4 never arrives: the waits of the other ranks run out, nothing hangs."""
     import time
     scratch = _scratch(cuda, 4)
     xs = [torch.ones(256 * 1024, dtype=torch.bfloat16, device=cuda) for _ in range(4)]
     t0 = time.time()
-    AR.all_reduce_emulated(xs, scratch, MAX_BYTES, absent_rank=2, protocol=3)
+    AR.all_reduce_emulated(xs, scratch, MAX_BYTES, absent_rank=2, protocol=protocol)
     torch.cuda.synchronize()
     assert time.time() - t0 < 10
     assert _lib.read_status() & 4, "NVLLM_STATUS_TIMEOUT expected"

@@ -116,8 +116,9 @@ def test_all_reduce_protocol_choice_is_host_arithmetic(lib):
     assert protocol_for(32 << 10, 2, mb) == "cells" and protocol_for(2 << 20, 2, mb) == "cells"
     assert protocol_for(4 << 20, 2, mb) == "one-shot"
     assert protocol_for(32 << 10, 8, mb) == "cells"
-    assert protocol_for(512 << 10, 8, mb) == "two-shot" and protocol_for(2 << 20, 4, mb) == "two-shot"
-    assert protocol_for((2 << 20) + 6, 8, mb) == "one-shot"          # 3 elements beyond a whole vector
+    assert protocol_for(512 << 10, 8, mb) == "cells-two-shot" and protocol_for(2 << 20, 4, mb) == "cells-two-shot"
+    assert protocol_for(2 << 20, 8, mb, forced=3) == "two-shot" and protocol_for(6 << 20, 4, mb) == "two-shot"
+    assert protocol_for((2 << 20) + 6, 8, mb) == "cells-two-shot"    # a ragged tail is fine for cells
     assert protocol_for(2 << 20, 8, mb, forced=2) == "one-shot"
     assert protocol_for(2 << 20, 2, mb, forced=3) == "cells"           # two shots need more than two ranks
-    assert protocol_for(2 << 20, 8, mb, forced=1) == "two-shot"        # cells do not fit: 2 x 2 MiB x 8 > 8 MiB
+    assert protocol_for(2 << 20, 8, mb, forced=1) == "cells-two-shot"  # cells to every peer do not fit: 2 x 2 MiB x 8 > 8 MiB
