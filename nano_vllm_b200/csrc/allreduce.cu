@@ -74,9 +74,11 @@ constexpr int64_t kHeaderBytes = 8192;
 static_assert(kCellEpochOff + kMaxBlocks * 4 <= kHeaderBytes, "header");
 constexpr int kAreas = 8;  // staging 0/1, cells 0/1, result 0/1, result cells 0/1: max_bytes each
 enum Protocol { kAuto = 0, kCells = 1, kOneShot = 2, kTwoShot = 3, kCellsTwoShot = 4 };
-// Above this size the flagged cells (twice the bytes on the wire, to every peer) lose against two
-// shots at more than two ranks.
-constexpr int64_t kCellsMaxBytesManyRanks = 128 << 10;
+// At more than two ranks, cells to every peer put 2 x bytes x (w-1) on a rank's wire, cells in two
+// shots 4 x bytes x (w-1)/w but cost one more NVLink crossing (about 6 us measured at 4 ranks).
+// The first wins while its extra bytes, bytes x (w-1) x (2 - 4/w), stay below this (measured
+// crossover at 4 ranks: between 512 KiB and 1 MiB).
+constexpr int64_t kCellsOneShotExtraBytes = 2 << 20;
 
 struct Peers {
   unsigned char* base[kMaxRanks];
@@ -505,7 +507,7 @@ __host__ __device__ inline int pick_protocol(int64_t n16, int64_t tail_elems, in
   if (force == kCellsTwoShot && cells_twoshot_fits) return kCellsTwoShot;
   if (force == kTwoShot && twoshot_fits) return kTwoShot;
   if (force == kOneShot) return kOneShot;
-  if (cells_fit && (world == 2 || n_elems * 2 <= kCellsMaxBytesManyRanks)) return kCells;
+  if (cells_fit && (world == 2 || n_elems * 2 * (world - 1) * (2 * world - 4) / world <= kCellsOneShotExtraBytes)) return kCells;
   if (cells_twoshot_fits) return kCellsTwoShot;
   if (twoshot_fits) return kTwoShot;
   return kOneShot;
