@@ -184,6 +184,30 @@ def lm_head_sample_ref(hidden, weight_shards, cu_seqlens_q, temperatures, noise)
     return sampler_ref(logits, temperatures, noise), logits
 
 
+def sample_candidates_ref(logits_slice, temperatures, noise_slice, vocab_offset):
+    """What one rank contributes to the vocabulary-sharded tail: for every row the best
+    (score, global index) of its slice, packed into an int64 whose signed order is "higher score,
+    then lower index" (score bits mapped order-preservingly into the high word, 2^32 - 1 - index in
+    the low word).  The element-wise maximum over the ranks, unpacked with
+    ``sample_unpack_ref``, is the token of ``sampler_ref`` on the concatenated logits."""
+    # A score that does not depend on the slice: softmax(x / T) / (e + 1e-10) has the same argmax
+    # as x / T - ln(e + 1e-10), the softmax maximum and normaliser being constants of the whole row.
+    x = logits_slice.to(torch.float32)
+    t = temperatures.to(torch.float32).unsqueeze(1)
+    race = x / t - torch.log(noise_slice.to(torch.float32) + 1e-10)
+    scores = torch.where(t == 0, x, race)
+    best = scores.max(dim=-1)
+    bits = best.values.contiguous().view(torch.int32).to(torch.int64)
+    ordered = torch.where(bits >= 0, bits, bits ^ 0x7FFFFFFF)
+    # ties inside the slice: torch.max returns the first maximal index on the CPU
+    idx = best.indices.to(torch.int64) + int(vocab_offset)
+    return (ordered << 32) | (0xFFFFFFFF - idx)
+
+
+def sample_unpack_ref(packed):
+    return 0xFFFFFFFF - (packed & 0xFFFFFFFF)
+
+
 # ---- decode-step inputs (nanovllm/engine/model_runner.py:151-159, 218-249, 271-282) ---------
 
 def decode_inputs_ref(seqs, graph_bs, table_width, block_size=BLOCK_SIZE):

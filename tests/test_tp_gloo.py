@@ -103,3 +103,43 @@ def test_ranks_exchange_handles_in_rank_order_and_agree_on_the_sum():
         assert p.exitcode == 0
     got = dict(result.get(timeout=5) for _ in range(2))
     assert got == {0: True, 1: True}
+
+
+def _lm_head_worker(rank, world, port, result):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.set_num_threads(2)
+        g = torch.Generator().manual_seed(77)                        # same on every rank
+        vocab, hidden, rows = 4096, 64, 6
+        weight = torch.randn(vocab, hidden, generator=g).to(torch.bfloat16)
+        x = torch.randn(rows, hidden, generator=g).to(torch.bfloat16)
+        temps = torch.tensor([0.0, 0.6, 1.0, 0.0, 0.3, 2.0])
+        noise = torch.empty(rows, vocab).exponential_(1, generator=g)
+        per = vocab // world
+        mine = torch.nn.functional.linear(x, weight[rank * per:(rank + 1) * per])   # this rank's slice of the logits
+        cand = R.sample_candidates_ref(mine, temps, noise[:, rank * per:(rank + 1) * per], rank * per)
+        dist.reduce(cand, dst=0, op=dist.ReduceOp.MAX)                # 8 bytes per row instead of the logits
+        if rank == 0:
+            want, _ = R.lm_head_sample_ref(x, list(weight.chunk(world, 0)), None, temps, noise)
+            result.put(R.sample_unpack_ref(cand).tolist() == want.tolist())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(120)
+def test_vocabulary_sharded_sampling_merges_to_the_unsharded_tokens():
+    """The tail of a tensor-parallel step, world_size 2 over gloo: every rank reduces its slice of
+    the logits to one packed candidate per row, a MAX reduction merges them, and rank 0 holds the
+    tokens that ParallelLMHead's gather + cat followed by the Sampler would have produced
+    (nanovllm/layers/embed_head.py:78-87, sampler.py:10-26)."""
+    ctx = mp.get_context("spawn")
+    result = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_lm_head_worker, args=(r, 2, port, result)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(100)
+        assert p.exitcode == 0
+    assert result.get(timeout=5) is True
