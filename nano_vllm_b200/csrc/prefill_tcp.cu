@@ -78,19 +78,6 @@ static_assert(P_NUM_BARS * 8 <= 256, "barrier area");
 __device__ unsigned int g_item_counter[tcp::NUM_SLOTS];
 __device__ unsigned int g_done_counter[tcp::NUM_SLOTS];
 
-#ifdef NVLLM_PREFILL_PROFILE
-// Development build only: where the first softmax warp of every block spends its cycles
-// (8 counters per block), read back through nvllm_debug_prefill_profile.
-__device__ unsigned long long g_prefill_prof[2048 * 8];
-#define PROF_DECL long long prof_t = clock64(); unsigned long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0}
-#define PROF(i) do { const long long now_ = clock64(); prof[i] += now_ - prof_t; prof_t = now_; } while (0)
-#define PROF_COUNT(i) (++prof[i])
-#else
-#define PROF_DECL
-#define PROF(i)
-#define PROF_COUNT(i)
-#endif
-
 struct Item {
   int b, h, m0, q0, Lq, k0, Lk, n_kv;  // n_kv < 0: no more work
 };
@@ -353,182 +340,147 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
     const int r_tok = r / pack;  // this row's token within the tile (== BMT for the unused rows of a 7-head tile)
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     unsigned char* stage = base_ptr + G::OFF_STAGE + warp * 2048;  // this warp's 32 rows x 64 B
-    // Output side of the epilogue: one store instruction writes eight 64-byte row segments;
-    // lane -> (row, 16-byte piece).  The four rows a lane stores never change: token and head of
-    // each, and its offset in the output, are worked out once.
-    const int srow = lane >> 2, spiece = lane & 3;
-    int st_off[4];      // a tile spans at most 128 output rows: the offsets fit 32 bits
-    uint32_t st_toks = 0;  // the four rows' tokens within the tile, 8 bits each
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int row = warp * 32 + i * 8 + srow;  // row of the tile
-      const int tok = row / pack;
-      st_toks |= static_cast<uint32_t>(tok) << (8 * i);
-      st_off[i] = tok * static_cast<int>(p.out_stride) + (row - tok * pack) * D + spiece * 8;
-    }
-    // the item whose epilogue is running
-    float epi_inv = 0.f;
-    __nv_bfloat16* epi_out = nullptr;
-    int epi_toks = 0;
-    // 32 columns of O (already in `o`) -> output rows; then starts the load of the next 32, or,
-    // after the last, releases O.
-    auto epilogue_chunk = [&](int c, uint32_t (&o)[32]) {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        uint4 v;
-        v.x = pack_bf16x2(__uint_as_float(o[8 * k]) * epi_inv, __uint_as_float(o[8 * k + 1]) * epi_inv);
-        v.y = pack_bf16x2(__uint_as_float(o[8 * k + 2]) * epi_inv, __uint_as_float(o[8 * k + 3]) * epi_inv);
-        v.z = pack_bf16x2(__uint_as_float(o[8 * k + 4]) * epi_inv, __uint_as_float(o[8 * k + 5]) * epi_inv);
-        v.w = pack_bf16x2(__uint_as_float(o[8 * k + 6]) * epi_inv, __uint_as_float(o[8 * k + 7]) * epi_inv);
-        *reinterpret_cast<uint4*>(stage + lane * 64 + ((k ^ ((lane >> 1) & 3)) << 4)) = v;
-      }
-      if (c + 1 < OCH) {
-        tmem_ld32(tmem_o + lane_addr + (c + 1) * 32, o);
-      } else {  // O has been read: the next item's first product may overwrite it
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(O_FREE));
-      }
-      __syncwarp();
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int lr = i * 8 + srow;  // row within the warp's 32
-        const uint4 v = *reinterpret_cast<const uint4*>(stage + lr * 64 + ((spiece ^ ((lr >> 1) & 3)) << 4));
-        if (static_cast<int>((st_toks >> (8 * i)) & 0xffu) < epi_toks) *reinterpret_cast<uint4*>(epi_out + st_off[i] + c * 32) = v;
-      }
-      __syncwarp();
-    };
     int T = 0;
     bool ok = true;
-    PROF_DECL;
-    // One key tile of an item: scores -> P.  Returns false when a wait gave up.
-    auto do_tile = [&](const Item& x, int j, float& m_used, float& l) -> bool {
-      const int qi = x.m0 + r_tok, off = x.Lk - x.Lq;
-      const int t = T + j, st = t & 1, ph = (t >> 1) & 1;
-      const uint32_t tmem_s = tmem + st * 64 + lane_addr;
-      if (!wait_or_abort(bar(QK_DONE0 + st), ph, abort_flag)) return false;
-      PROF(1);  // waiting for the scores
-      PROF_COUNT(7);
-      tc_fence_after();
-      uint32_t s[64];
-      tmem_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-      tmem_ld32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
-      tmem_wait_ld();
-
-      const int j0 = j * BN;
-      if ((j0 + BN - 1 > x.m0 + off) || (j0 + BN > x.Lk)) {  // tile touches the diagonal or the end
-        const int limit = min(qi + off, x.Lk - 1) - j0;        // columns c <= limit are visible
-#pragma unroll
-        for (int c = 0; c < 64; ++c)
-          if (c > limit) s[c] = 0xff800000u;  // -inf
-      }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < 64; c += 8) {
-        mx4[0] = fmax3(mx4[0], __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
-        mx4[1] = fmax3(mx4[1], __uint_as_float(s[c + 2]), __uint_as_float(s[c + 3]));
-        mx4[2] = fmax3(mx4[2], __uint_as_float(s[c + 4]), __uint_as_float(s[c + 5]));
-        mx4[3] = fmax3(mx4[3], __uint_as_float(s[c + 6]), __uint_as_float(s[c + 7]));
-      }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      const float m_new = fmaxf(m_used, mx * p.scale_log2e);
-      // lazy rescale: keep the old reference maximum unless it has been outgrown by 2^8
-      const bool grow = m_new > m_used + kRescaleThreshold;
-      if (__any_sync(0xffffffffu, grow)) {
-        float alpha = 1.f;
-        if (grow) {
-          alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
-          m_used = m_new;
-          l *= alpha;
-        }
-        if (j > 0) {  // O holds tiles 0..j-1 of this item once the previous P V product has finished
-          PROF(2);
-          if (!wait_or_abort(bar(PV_DONE0 + ((t - 1) & 1)), ((t - 1) >> 1) & 1, abort_flag)) return false;
-          PROF(3);  // waiting for O before a rescale
-          tc_fence_after();
-#pragma unroll
-          for (int c = 0; c < OCH; ++c) {
-            uint32_t o[32];
-            tmem_ld32(tmem_o + lane_addr + c * 32, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-            tmem_st32(tmem_o + lane_addr + c * 32, o);
-          }
-        }
-      }
-      const float msub = (m_used == -INFINITY) ? 0.f : m_used;
-      // p = 2^(s * scale - m): the multiply-subtract and the row sum run two lanes at a time
-      const uint64_t scale2 = pack2(p.scale_log2e, p.scale_log2e), nmsub2 = pack2(-msub, -msub);
-      uint64_t sum2[2] = {0ull, 0ull};
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {  // P is packed in place: s[c] <- (p[2c], p[2c+1])
-        float a0, a1;
-        unpack2(fma2(pack2(__uint_as_float(s[2 * c]), __uint_as_float(s[2 * c + 1])), scale2, nmsub2), a0, a1);
-        const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
-        sum2[c & 1] = add2(sum2[c & 1], pack2(p0, p1));
-        s[c] = pack_bf16x2(p0, p1);
-      }
-      {
-        float t0, t1, t2, t3;
-        unpack2(sum2[0], t0, t1);
-        unpack2(sum2[1], t2, t3);
-        l += (t0 + t1) + (t2 + t3);
-      }
-      if (j0 + BN > x.Lk) {
-        // Last tile of the sequence: V rows past the end hold whatever the cache block (or the
-        // next sequence) has there.  Their P is 0, but 0 x NaN would still poison O, so the
-        // rows are cleared in shared memory before the product is issued.
-        if (!wait_or_abort(bar(V_FULL0 + st), ph, abort_flag)) return false;
-        const int first = x.Lk - j0;  // rows [first, 64) are dead
-        unsigned char* vt = base_ptr + OFF_V + st * KV_BYTES;
-        for (int i = r; i < (BN - first) * PIECES; i += 128) {
-          const int row = first + i / PIECES, piece = i % PIECES;
-          *reinterpret_cast<uint4*>(vt + (piece >> 3) * KV_SUB + row * 128 + (piece & 7) * 16) = make_uint4(0, 0, 0, 0);
-        }
-        fence_proxy_async();
-      }
-      tmem_st32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
-      tmem_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(P_FULL0 + st));
-      PROF(2);  // softmax of one tile
-      return true;
-    };
     for (int it = 0; ok; ++it) {
       if (!(ok = wait_or_abort(bar(ITEM_FULL0 + (it & 1)), (it >> 1) & 1, abort_flag))) break;
       const Item x = read_item(it);
-      PROF(0);  // waiting for the next item
       if (x.n_kv < 0) break;
-      PROF_COUNT(6);
+      const int qi = x.m0 + r_tok, off = x.Lk - x.Lq;
       float m_used = -INFINITY, l = 0.f;
-      for (int j = 0; j < x.n_kv; ++j)
-        if (!(ok = do_tile(x, j, m_used, l))) break;
+      for (int j = 0; j < x.n_kv; ++j) {
+        const int t = T + j, st = t & 1, ph = (t >> 1) & 1;
+        const uint32_t tmem_s = tmem + st * 64 + lane_addr;
+        if (!(ok = wait_or_abort(bar(QK_DONE0 + st), ph, abort_flag))) break;
+        tc_fence_after();
+        uint32_t s[64];
+        tmem_ld32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        tmem_ld32(tmem_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&s[32]));
+        tmem_wait_ld();
+
+        const int j0 = j * BN;
+        if ((j0 + BN - 1 > x.m0 + off) || (j0 + BN > x.Lk)) {  // tile touches the diagonal or the end
+          const int limit = min(qi + off, x.Lk - 1) - j0;        // columns c <= limit are visible
+#pragma unroll
+          for (int c = 0; c < 64; ++c)
+            if (c > limit) s[c] = 0xff800000u;  // -inf
+        }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 64; c += 8) {
+          mx4[0] = fmax3(mx4[0], __uint_as_float(s[c]), __uint_as_float(s[c + 1]));
+          mx4[1] = fmax3(mx4[1], __uint_as_float(s[c + 2]), __uint_as_float(s[c + 3]));
+          mx4[2] = fmax3(mx4[2], __uint_as_float(s[c + 4]), __uint_as_float(s[c + 5]));
+          mx4[3] = fmax3(mx4[3], __uint_as_float(s[c + 6]), __uint_as_float(s[c + 7]));
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        const float m_new = fmaxf(m_used, mx * p.scale_log2e);
+        // lazy rescale: keep the old reference maximum unless it has been outgrown by 2^8
+        const bool grow = m_new > m_used + kRescaleThreshold;
+        if (__any_sync(0xffffffffu, grow)) {
+          float alpha = 1.f;
+          if (grow) {
+            alpha = (m_used == -INFINITY) ? 0.f : fast_exp2(m_used - m_new);
+            m_used = m_new;
+            l *= alpha;
+          }
+          if (j > 0) {  // O holds tiles 0..j-1 of this item once the previous P V product has finished
+            if (!(ok = wait_or_abort(bar(PV_DONE0 + ((t - 1) & 1)), ((t - 1) >> 1) & 1, abort_flag))) break;
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < OCH; ++c) {
+              uint32_t o[32];
+              tmem_ld32(tmem_o + lane_addr + c * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+              tmem_st32(tmem_o + lane_addr + c * 32, o);
+            }
+          }
+        }
+        const float msub = (m_used == -INFINITY) ? 0.f : m_used;
+        // p = 2^(s * scale - m): the multiply-subtract and the row sum run two lanes at a time
+        const uint64_t scale2 = pack2(p.scale_log2e, p.scale_log2e), nmsub2 = pack2(-msub, -msub);
+        uint64_t sum2[2] = {0ull, 0ull};
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {  // P is packed in place: s[c] <- (p[2c], p[2c+1])
+          float a0, a1;
+          unpack2(fma2(pack2(__uint_as_float(s[2 * c]), __uint_as_float(s[2 * c + 1])), scale2, nmsub2), a0, a1);
+          const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
+          sum2[c & 1] = add2(sum2[c & 1], pack2(p0, p1));
+          s[c] = pack_bf16x2(p0, p1);
+        }
+        {
+          float t0, t1, t2, t3;
+          unpack2(sum2[0], t0, t1);
+          unpack2(sum2[1], t2, t3);
+          l += (t0 + t1) + (t2 + t3);
+        }
+        if (j0 + BN > x.Lk) {
+          // Last tile of the sequence: V rows past the end hold whatever the cache block (or the
+          // next sequence) has there.  Their P is 0, but 0 x NaN would still poison O, so the
+          // rows are cleared in shared memory before the product is issued.
+          if (!(ok = wait_or_abort(bar(V_FULL0 + st), ph, abort_flag))) break;
+          const int first = x.Lk - j0;  // rows [first, 64) are dead
+          unsigned char* vt = base_ptr + OFF_V + st * KV_BYTES;
+          for (int i = r; i < (BN - first) * PIECES; i += 128) {
+            const int row = first + i / PIECES, piece = i % PIECES;
+            *reinterpret_cast<uint4*>(vt + (piece >> 3) * KV_SUB + row * 128 + (piece & 7) * 16) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async();
+        }
+        tmem_st32(tmem_s, *reinterpret_cast<uint32_t(*)[32]>(&s[0]));
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(P_FULL0 + st));
+      }
       if (!ok) break;
       T += x.n_kv;
 
       // epilogue: O / l -> bf16; 32 columns at a time through this warp's patch of shared memory
       if (!(ok = wait_or_abort(bar(PV_DONE0 + ((T - 1) & 1)), ((T - 1) >> 1) & 1, abort_flag))) break;
-      PROF(4);  // waiting for the last product before the epilogue
       tc_fence_after();
-      epi_inv = l > 0.f ? 1.f / l : 0.f;
-      epi_out = p.out + static_cast<int64_t>(x.q0 + x.m0) * p.out_stride + x.h * D;
-      epi_toks = min(BMT, x.Lq - x.m0);
-      uint32_t ob[32];
-      tmem_ld32(tmem_o + lane_addr, ob);
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      // lane -> (row, 16-byte piece) of the eight 64-byte row segments one store instruction writes
+      const int srow = lane >> 2, spiece = lane & 3;
+      __nv_bfloat16* out_tile = p.out + static_cast<int64_t>(x.q0 + x.m0) * p.out_stride + x.h * D;
+      const int toks_valid = min(BMT, x.Lq - x.m0);
+      uint32_t ob[2][32];  // the load of the next 32 columns runs under the stores of the current ones
+      tmem_ld32(tmem_o + lane_addr, ob[0]);
 #pragma unroll
       for (int c = 0; c < OCH; ++c) {
+        uint32_t(&o)[32] = ob[c & 1];
         tmem_wait_ld();
-        epilogue_chunk(c, ob);  // starts the load of the next 32 columns; releases O after the last
+        if (c + 1 < OCH) tmem_ld32(tmem_o + lane_addr + (c + 1) * 32, ob[(c + 1) & 1]);
+        if (c == OCH - 1) {  // O is in registers: the next item's first product may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(O_FREE));
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          uint4 v;
+          v.x = pack_bf16x2(__uint_as_float(o[8 * k]) * inv, __uint_as_float(o[8 * k + 1]) * inv);
+          v.y = pack_bf16x2(__uint_as_float(o[8 * k + 2]) * inv, __uint_as_float(o[8 * k + 3]) * inv);
+          v.z = pack_bf16x2(__uint_as_float(o[8 * k + 4]) * inv, __uint_as_float(o[8 * k + 5]) * inv);
+          v.w = pack_bf16x2(__uint_as_float(o[8 * k + 6]) * inv, __uint_as_float(o[8 * k + 7]) * inv);
+          *reinterpret_cast<uint4*>(stage + lane * 64 + ((k ^ ((lane >> 1) & 3)) << 4)) = v;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int lr = i * 8 + srow;       // row within the warp's 32
+          const int row = warp * 32 + lr;    // row of the tile
+          const int tok = row / pack, hh = row - tok * pack;
+          const uint4 v = *reinterpret_cast<const uint4*>(stage + lr * 64 + ((spiece ^ ((lr >> 1) & 3)) << 4));
+          if (tok < toks_valid)
+            *reinterpret_cast<uint4*>(out_tile + static_cast<int64_t>(tok) * p.out_stride + hh * D + c * 32 + spiece * 8) = v;
+        }
+        __syncwarp();
       }
       if (lane == 0) mbar_arrive(bar(ITEM_FREE0 + (it & 1)));
-      PROF(5);  // epilogue
     }
-#ifdef NVLLM_PREFILL_PROFILE
-    if (tid == 0 && blockIdx.x < 2048)
-      for (int i = 0; i < 8; ++i) g_prefill_prof[blockIdx.x * 8 + i] = prof[i];
-#endif
   }
 
   tc_fence_before();
@@ -595,13 +547,6 @@ static int launch_prefill_tcp_t(const PrefillParams& p_in, int64_t total_q, int6
   count_launch();
   return check_launch("prefill (tcgen05, persistent) launch");
 }
-
-#ifdef NVLLM_PREFILL_PROFILE
-extern "C" NVLLM_API int nvllm_debug_prefill_profile(unsigned long long* host_out, int n_blocks) {
-  if (n_blocks > 2048) n_blocks = 2048;
-  return cudaMemcpyFromSymbol(host_out, g_prefill_prof, sizeof(unsigned long long) * 8 * n_blocks) == cudaSuccess ? 0 : -5;
-}
-#endif
 
 int launch_prefill_tcp(const PrefillParams& p, int64_t total_q, int64_t total_k, cudaStream_t stream) {
   if (p.d == 128) return launch_prefill_tcp_t<128>(p, total_q, total_k, stream);
