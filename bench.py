@@ -76,8 +76,8 @@ def parse_args():
                     help="skip the end-to-end nano-vllm engine runs (output tok/s) that close the line")
     ap.add_argument("--kernel", default=None,
                     choices=["prefill", "prefill_long", "prefill_d64", "store", "decode", "decode_tp8", "decode_engine",
-                             "decode_long", "sampler", "allreduce"],
-                    help="time only this kernel and print its line (profiling aid; allreduce runs under torchrun)")
+                             "decode_long", "sampler", "allreduce", "gemm_allreduce"],
+                    help="time only this kernel and print its line (profiling aid; allreduce and gemm_allreduce run under torchrun)")
     ap.add_argument("--ar-protocol", type=int, default=0, choices=[0, 1, 2, 3, 4],
                     help="with --kernel allreduce: force a protocol (0 automatic, 1 cells, 2 one shot, 3 two shots, "
                          "4 cells in two shots)")
@@ -773,9 +773,84 @@ def run_allreduce(args):
     dist.destroy_process_group()
 
 
+def run_gemm_allreduce(args):
+    """The row-parallel projection and its sum as one launch (PeerAllReduce.linear_all_reduce) next
+    to the pairs it replaces -- torch's F.linear followed by the peer-memory all-reduce, and by
+    NCCL's -- on the o_proj / down_proj shapes of a decode step; run under torchrun, one process
+    per GPU, every variant replayed from a CUDA graph, max over ranks.  Rank 0 prints one JSON line
+    per shape."""
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from nano_vllm_b200 import _lib
+    from nano_vllm_b200.allreduce import PeerAllReduce
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    build_once(local, dist.barrier)
+    iters = args.steps
+
+    def timed_graph(fn, calls=8):
+        g = torch.cuda.CUDAGraph()
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            fn()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g, stream=s):
+                for _ in range(calls):
+                    fn()
+        for _ in range(5):
+            g.replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n = iters // calls + 1
+        a.record()
+        for _ in range(n):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / (n * calls) * 1e3], device="cuda")  # us per call
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return round(float(t), 2)
+
+    ar = PeerAllReduce(rank, world, 8 << 20, wait_ms=20000)
+    shapes = [(name, tokens, hidden, k_total // world)
+              for name, hidden, k_total in (("qwen3-8b o_proj", 4096, 4096), ("qwen3-8b down_proj", 4096, 12288),
+                                            ("qwen3-0.6b o_proj", 1024, 2048), ("qwen3-0.6b down_proj", 1024, 3072))
+              for tokens in (16, 64, 256)]
+    for name, m, n, k in shapes:
+        g = torch.Generator().manual_seed(1 + rank)
+        x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+        w = (torch.randn(n, k, generator=g) * (k * world) ** -0.5).to(torch.bfloat16).cuda()
+        if not ar.linear_fits(x, w):
+            continue
+        fused = ar.linear_all_reduce(x, w)
+        pair = ar.all_reduce(F.linear(x, w))
+        torch.cuda.synchronize()
+        out = torch.empty_like(fused)
+        line = {"kernel": "gemm_allreduce", "layer": name, "tokens": m, "n": n, "k_per_rank": k, "world": world,
+                "max_abs_diff_vs_pair": float((fused.float() - pair.float()).abs().max()),
+                "out_abs_max": float(pair.float().abs().max())}
+        line["fused_us"] = timed_graph(lambda: ar.linear_all_reduce(x, w, out))
+        line["linear_us"] = timed_graph(lambda: F.linear(x, w))
+        line["linear_peer_us"] = timed_graph(lambda: ar.all_reduce(F.linear(x, w)))
+        line["linear_nccl_us"] = timed_graph(lambda: dist.all_reduce(F.linear(x, w)))
+        line["status"] = _lib.read_status()
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+    dist.barrier()
+    ar.close()
+    dist.destroy_process_group()
+
+
 def run_one_kernel(args):
     if args.kernel == "allreduce":
         return run_allreduce(args)
+    if args.kernel == "gemm_allreduce":
+        return run_gemm_allreduce(args)
     import torch
     from nano_vllm_b200 import build as _build
     _build.build()

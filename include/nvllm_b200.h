@@ -339,6 +339,30 @@ NVLLM_API int nvllm_ar_allreduce_emulated(int32_t world, const void* const* inpu
                                 int64_t n_elems, void* scratch, int64_t scratch_bytes, int64_t max_bytes,
                                 int32_t absent_rank, int32_t protocol, void* stream);
 
+/* Row-parallel projection fused with its all-reduce: out[m, n] = sum over ranks of x_r[m, k] w_r[n, k]^T,
+ * bf16 in and out.  Replaces F.linear followed by dist.all_reduce in RowParallelLinear.forward
+ * (nanovllm/layers/linear.py:195-199) for bias-free projections of decode-sized batches: ONE launch
+ * per rank computes the rank's partial on the tcgen05 tensor cores (TMA-fed, accumulator in TMEM)
+ * and its epilogue sums the partials over peer memory tile by tile -- each rank's fp32 partial is
+ * rounded to bf16 (as F.linear would have), a tile's partials go to the tile's owner rank as
+ * flagged cells, the owner adds them in rank order in fp32, rounds once and sends the result to
+ * every rank, so all ranks hold the same bits.  Needs nvllm_ar_init + nvllm_ar_connect; every rank
+ * makes the same calls in the same order, and calls may be mixed freely with nvllm_ar_allreduce.
+ * x, weight, out: 16-byte aligned, row strides (elements) multiples of 8; k a multiple of 8, n of 32.
+ * nvllm_ar_gemm_tile() returns the tile width (32, 64 or 128) the call would use, or 0 when the
+ * shape does not fit the cell areas (4 * n * 128 * ceil(m / 128) bytes needed out of max_bytes) or
+ * has fewer tiles than ranks; such shapes are refused with NVLLM_E_GEOMETRY (use the unfused pair).
+ * Pure host arithmetic; no device needed. */
+NVLLM_API int nvllm_ar_gemm_tile(int64_t m, int64_t n, int64_t k, int32_t world, int64_t max_bytes);
+NVLLM_API int nvllm_ar_gemm_allreduce(const void* x, int64_t x_stride, const void* weight, int64_t w_stride, void* out,
+                            int64_t out_stride, int64_t m, int64_t n, int64_t k, void* stream);
+/* The same with all ranks emulated by ONE cooperative launch on the current device (xs[r] [m, k],
+ * weights[r] [n, k], outputs[r] [m, n], all contiguous; scratch as for nvllm_ar_allreduce_emulated).
+ * No counterpart in the reference. */
+NVLLM_API int nvllm_ar_gemm_allreduce_emulated(int32_t world, const void* const* xs, const void* const* weights,
+                                     void* const* outputs, int64_t m, int64_t n, int64_t k, void* scratch,
+                                     int64_t scratch_bytes, int64_t max_bytes, void* stream);
+
 /* Known-answer check of the tensor-core building blocks the prefill kernel is made of
  * (TMA swizzled loads, shared-memory and instruction descriptors, TMEM loads and stores):
  * out_ss = A B^T and out_ts = A B for A, B [128,128] bf16 row-major, outputs [128,128] fp32.

@@ -54,6 +54,11 @@ SIGNATURES = {
     "nvllm_ar_emulated_scratch_bytes": (c_int64, [c_int32, c_int64]),
     "nvllm_ar_allreduce_emulated": (c_int32, [c_int32, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int32,
                                               c_int32, c_void_p]),
+    "nvllm_ar_gemm_tile": (c_int32, [c_int64, c_int64, c_int64, c_int32, c_int64]),
+    "nvllm_ar_gemm_allreduce": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64,
+                                          c_int64, c_void_p]),
+    "nvllm_ar_gemm_allreduce_emulated": (c_int32, [c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                                   c_void_p, c_int64, c_int64, c_void_p]),
     "nvllm_selftest_umma": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvllm_selftest_wait_expiry": (c_int32, [c_void_p, c_void_p]),
     "nvllm_last_error": (c_char_p, []),

@@ -84,6 +84,31 @@ class PeerAllReduce:
                                                       torch.cuda.current_stream(x.device).cuda_stream))
         return x
 
+    def linear_fits(self, x: torch.Tensor, weight: torch.Tensor) -> bool:
+        """Whether ``linear_all_reduce(x, weight)`` can run: 2-D bf16 CUDA operands with 16-byte
+        aligned rows and a shape the fused kernel's cell areas hold (decode-sized batches)."""
+        if not (x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and weight.dim() == 2
+                and weight.dtype == torch.bfloat16 and x.shape[1] == weight.shape[1]
+                and x.stride(1) == 1 and weight.stride(1) == 1 and x.stride(0) % 8 == 0 and weight.stride(0) % 8 == 0
+                and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
+            return False
+        return _lib.load().nvllm_ar_gemm_tile(x.shape[0], weight.shape[0], x.shape[1], self.world, self.max_bytes) > 0
+
+    def linear_all_reduce(self, x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """``all_reduce(F.linear(x, weight))`` as one launch: ``x`` [tokens, in / ranks], ``weight``
+        [out, in / ranks] (this rank's shard of a row-parallel projection), result [tokens, out]."""
+        if not self.linear_fits(x, weight):
+            raise RuntimeError("PeerAllReduce.linear_all_reduce: shape or layout not supported (see linear_fits)")
+        m, k = x.shape
+        n = weight.shape[0]
+        if out is None:
+            out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+        with torch.cuda.device(x.device):
+            _lib.check(_lib.load().nvllm_ar_gemm_allreduce(x.data_ptr(), x.stride(0), weight.data_ptr(), weight.stride(0),
+                                                           out.data_ptr(), out.stride(0), m, n, k,
+                                                           torch.cuda.current_stream(x.device).cuda_stream))
+        return out
+
     def close(self) -> None:
         _lib.check(_lib.load().nvllm_ar_shutdown())
 
@@ -101,4 +126,22 @@ def all_reduce_emulated(inputs: list[torch.Tensor], scratch: torch.Tensor, max_b
             world, arr(*[x.data_ptr() for x in inputs]), arr(*[o.data_ptr() for o in outs]), inputs[0].numel(),
             scratch.data_ptr(), scratch.numel(), max_bytes, absent_rank, protocol,
             torch.cuda.current_stream(inputs[0].device).cuda_stream))
+    return outs
+
+
+def linear_all_reduce_emulated(xs: list[torch.Tensor], weights: list[torch.Tensor], scratch: torch.Tensor,
+                               max_bytes: int) -> list[torch.Tensor]:
+    """The fused projection + all-reduce of every rank in one cooperative launch on one device
+    (test aid): ``xs[r]`` [m, k], ``weights[r]`` [n, k] contiguous; returns one [m, n] output per
+    rank.  ``scratch`` as for ``all_reduce_emulated`` (the two may share it)."""
+    world = len(xs)
+    m, k = xs[0].shape
+    n = weights[0].shape[0]
+    outs = [torch.empty(m, n, dtype=torch.bfloat16, device=xs[0].device) for _ in range(world)]
+    arr = ctypes.c_void_p * world
+    with torch.cuda.device(xs[0].device):
+        _lib.check(_lib.load().nvllm_ar_gemm_allreduce_emulated(
+            world, arr(*[x.data_ptr() for x in xs]), arr(*[w.data_ptr() for w in weights]),
+            arr(*[o.data_ptr() for o in outs]), m, n, k, scratch.data_ptr(), scratch.numel(), max_bytes,
+            torch.cuda.current_stream(xs[0].device).cuda_stream))
     return outs

@@ -57,32 +57,10 @@
 
 #include <cstring>
 
-#include "common.cuh"
-#include "sm100.cuh"
+#include "allreduce.cuh"
 
 namespace nvllm {
 namespace ar {
-
-constexpr int kMaxRanks = 8;
-constexpr int kMaxBlocks = 128;
-constexpr int kThreads = 512;
-constexpr int64_t kFlagBytes = kMaxBlocks * kMaxRanks * 4;
-constexpr int64_t kEpochOff = kFlagBytes;                      // u32[kMaxBlocks]
-constexpr int64_t kBrokenOff = kEpochOff + kMaxBlocks * 4;     // u32 latch
-constexpr int64_t kCellEpochOff = kBrokenOff + 64;             // u32[kMaxBlocks], call counts of the cell protocol
-constexpr int64_t kHeaderBytes = 8192;
-static_assert(kCellEpochOff + kMaxBlocks * 4 <= kHeaderBytes, "header");
-constexpr int kAreas = 8;  // staging 0/1, cells 0/1, result 0/1, result cells 0/1: max_bytes each
-enum Protocol { kAuto = 0, kCells = 1, kOneShot = 2, kTwoShot = 3, kCellsTwoShot = 4 };
-// At more than two ranks, cells to every peer put 2 x bytes x (w-1) on a rank's wire, cells in two
-// shots 4 x bytes x (w-1)/w but cost one more NVLink crossing (about 6 us measured at 4 ranks).
-// The first wins while its extra bytes, bytes x (w-1) x (2 - 4/w), stay below this (measured
-// crossover at 4 ranks: between 512 KiB and 1 MiB).
-constexpr int64_t kCellsOneShotExtraBytes = 2 << 20;
-
-struct Peers {
-  unsigned char* base[kMaxRanks];
-};
 
 struct Params {
   const uint4* in;
@@ -96,40 +74,6 @@ struct Params {
   Peers peers;
   int* status;
 };
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ uint4 ld_volatile16(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
-}
-__device__ __forceinline__ void st_volatile16(uint4* p, const uint4& v) {
-  asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-__device__ __forceinline__ void add4(float (&acc)[4], uint32_t lo, uint32_t hi) {
-  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&lo));
-  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&hi));
-  acc[0] += a.x;
-  acc[1] += a.y;
-  acc[2] += b.x;
-  acc[3] += b.y;
-}
-__device__ __forceinline__ void add8(float (&acc)[8], const uint4& v) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 f = __bfloat1622float2(h[i]);
-    acc[2 * i] += f.x;
-    acc[2 * i + 1] += f.y;
-  }
-}
 
 // The work of block `b` (of `nblocks`) on behalf of rank `rank`.
 __device__ void allreduce_block(const Params& p, int rank, int b, int nblocks) {
@@ -543,19 +487,10 @@ __global__ void __launch_bounds__(kThreads) allreduce_emulated_kernel(const EmuP
   allreduce_dispatch(p, rank, blockIdx.x, gridDim.x);
 }
 
-// ---- host state (one per device of this process) ---------------------------------------------
-struct State {
-  bool ready = false, connected = false;
-  int rank = 0, world = 0;
-  int force = kAuto;
-  int64_t stage_bytes = 0;
-  long long wait_cycles = sm100::kWaitLimitCycles;
-  unsigned char* own = nullptr;
-  Peers peers{};
-};
+// ---- host state (one per device of this process): declared in allreduce.cuh -----------------
 static State g_state[64];
 
-static State* current_state() {
+State* current_state() {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
     (void)cudaGetLastError();
@@ -564,13 +499,6 @@ static State* current_state() {
   return &g_state[dev];
 }
 
-// Every call uses the same grid, whatever the size: the blocks' call counts then advance in
-// lock-step, so all blocks of a call use the same staging buffer and the two-buffer argument
-// above holds for the whole tensor (a block whose slice is empty still takes part in the
-// hand-shake).
-constexpr int kGrid = 128;
-constexpr int kEmulatedGrid = 16;  // x ranks blocks must be resident together on one device
-static_assert(kGrid <= kMaxBlocks, "flag slots");
 
 }  // namespace ar
 }  // namespace nvllm

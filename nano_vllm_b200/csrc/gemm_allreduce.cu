@@ -1,0 +1,418 @@
+// Row-parallel projection and its all-reduce as ONE kernel: Y = sum over ranks of X_r W_r^T.
+//
+// nano-vllm's RowParallelLinear (nanovllm/layers/linear.py:176-199) computes F.linear on every
+// tensor-parallel rank and sums the partial outputs with dist.all_reduce: two launches and a pass
+// of the [tokens, hidden] partial through HBM.  Here the product runs on the tcgen05 tensor cores
+// (operands by TMA tile loads into a ring of shared-memory stages, accumulator in TMEM) and the
+// epilogue that reads the accumulator IS the all-reduce, in the flagged-cell two-shot protocol of
+// allreduce.cu, tile by tile:
+//
+//   * the output is cut into tiles of 128 rows x bn columns (bn = 32, 64 or 128, the smallest
+//     that leaves at most one tile per thread block); tile t is owned by rank t mod world;
+//   * every rank rounds its fp32 partial of a tile to bf16 (what F.linear would have returned);
+//     a rank that does not own the tile pushes it as cells {d0, call count, d1, call count}
+//     straight from registers into the owner's cell area, region [tile slot][source rank];
+//   * the owner adds the partials in rank order in fp32 as the cells arrive, rounds once, writes
+//     its own output and pushes the result cells into every peer's result-cell area;
+//   * the other ranks copy the tile from their result-cell area to their output.
+// A cell of a tile lives at (column group * 128 + row) * 16 bytes, so the 32 lanes of a warp
+// (32 consecutive accumulator rows) write 512 contiguous bytes per store instruction.
+//
+// The kernel uses the same grid, the same per-block call counts and the same two alternating cell
+// areas as the cell protocols of the plain all-reduce, so calls of either kind may follow each
+// other in any order (the same order on every rank).  All waits are bounded: on expiry the status
+// word gets NVLLM_STATUS_TIMEOUT, the latch in the rank's area makes later calls give up at once,
+// and the block frees its tensor memory and ends normally.  Peer memory is only touched by plain
+// 16-byte stores issued by each thread; TMA loads read this rank's own X and W.
+#include <cooperative_groups.h>
+
+#include "allreduce.cuh"
+#include "prefill_tc.cuh"
+
+namespace nvllm {
+namespace gar {
+using namespace sm100;
+using namespace ar;
+
+constexpr int BM = 128, BK = 64, NST = 6, NTHREADS = 192;
+constexpr int A_BYTES = BM * BK * 2;        // 16 KB: one 128-byte-swizzled [128 x 64] sub-tile
+constexpr int STAGE_BYTES = 2 * A_BYTES;    // X tile + room for a W tile of up to 128 rows
+constexpr int OFF_CTRL = NST * STAGE_BYTES;
+constexpr int SMEM = OFF_CTRL + 256 + 1024;  // + barriers, misc + alignment slack
+enum Bar { FULL0 = 0, EMPTY0 = NST, ACC_FULL = 2 * NST, ACC_FREE, DRAIN, NUM_BARS };
+static_assert(NUM_BARS * 8 <= 192, "barrier area");
+
+struct Maps {
+  CUtensorMap x[kMaxRanks];  // [m, k] activations of each rank (one entry unless emulated)
+  CUtensorMap w[kMaxRanks];  // [n, k] weight shard of each rank
+};
+
+struct Params {
+  __nv_bfloat16* out[kMaxRanks];
+  int64_t out_stride;  // elements between output rows
+  int m, n, k, bn;
+  int rank;            // >= 0: this process's rank; < 0: emulated, rank = blockIdx.x / nblocks
+  int world, nblocks;  // thread blocks per rank
+  int64_t stage_bytes;
+  long long wait_cycles;
+  Peers peers;
+  int* status;
+};
+
+__global__ void __launch_bounds__(NTHREADS, 1) gemm_allreduce_kernel(const __grid_constant__ Maps maps, const Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int rank = p.rank >= 0 ? p.rank : static_cast<int>(blockIdx.x) / p.nblocks;
+  const int b = p.rank >= 0 ? static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x) % p.nblocks;
+  const int mi = p.rank >= 0 ? 0 : rank;  // which tensor maps
+  const int w = p.world, bn = p.bn;
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bars = base + OFF_CTRL;
+  auto bar = [&](int i) { return bars + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + OFF_CTRL + 192);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + OFF_CTRL + 200);
+  volatile uint32_t* s_epoch = reinterpret_cast<volatile uint32_t*>(base_ptr + OFF_CTRL + 204);
+  volatile int* s_broken = reinterpret_cast<volatile int*>(base_ptr + OFF_CTRL + 208);
+
+  unsigned char* own = p.peers.base[rank];
+  uint32_t* epochs = reinterpret_cast<uint32_t*>(own + kCellEpochOff);
+  uint32_t* broken = reinterpret_cast<uint32_t*>(own + kBrokenOff);
+
+  const int ntn = p.n / bn, ntm = (p.m + BM - 1) / BM, tiles = ntn * ntm;
+  const int nkb = (p.k + BK - 1) / BK;
+  const bool has_work = b < tiles;
+
+  if (tid == 0) {
+    *s_epoch = epochs[b] + 1;
+    *s_broken = *reinterpret_cast<volatile uint32_t*>(broken) != 0;
+    *abort_flag = 0;
+    for (int i = 0; i < NUM_BARS; ++i) mbar_init(bar(i), i == ACC_FREE ? 4u : 1u);
+    mbar_fence_init();
+    prefetch_tmap(&maps.x[mi]);
+    prefetch_tmap(&maps.w[mi]);
+  }
+  const uint32_t tmem_cols = bn < 32 ? 32u : static_cast<uint32_t>(bn);
+  if (warp == 5 && has_work) tmem_alloc(smem_u32(tmem_slot), tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t e = *s_epoch;
+  if (!has_work) {  // nothing to compute: the call is still counted
+    if (tid == 0) epochs[b] = e;
+    return;
+  }
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int g = 0;  // k-blocks loaded so far in this block's life
+      bool ok = true;
+      for (int t = b; t < tiles && ok; t += p.nblocks) {
+        const int mt = t / ntn, nt = t - mt * ntn;
+        for (int kb = 0; kb < nkb; ++kb, ++g) {
+          const int s = g % NST, use = g / NST;
+          if (use > 0 && !(ok = wait_or_abort(bar(EMPTY0 + s), (use - 1) & 1, abort_flag))) break;
+          mbar_expect_tx(bar(FULL0 + s), A_BYTES + bn * 128);
+          tma_load_3d(base + s * STAGE_BYTES, &maps.x[mi], bar(FULL0 + s), kb * BK, 0, mt * BM);
+          tma_load_3d(base + s * STAGE_BYTES + A_BYTES, &maps.w[mi], bar(FULL0 + s), kb * BK, 0, nt * bn);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(BM, bn, 0, 0);
+      int g = 0, i = 0;
+      bool ok = true;
+      for (int t = b; t < tiles && ok; t += p.nblocks, ++i) {
+        // the accumulator is overwritten: the previous tile must have been read out
+        if (i > 0 && !(ok = wait_or_abort(bar(ACC_FREE), (i - 1) & 1, abort_flag))) break;
+        tc_fence_after();
+        for (int kb = 0; kb < nkb; ++kb, ++g) {
+          const int s = g % NST, use = g / NST;
+          if (!(ok = wait_or_abort(bar(FULL0 + s), use & 1, abort_flag))) break;
+          tc_fence_after();
+          const uint32_t a = base + s * STAGE_BYTES, bsm = a + A_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < BK / 16; ++ks)
+            umma_ss(tmem, umma_desc(a + ks * 32, 16, 1024), umma_desc(bsm + ks * 32, 16, 1024), idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+          umma_commit(bar(EMPTY0 + s));  // the stage is free once these products have read it
+        }
+        if (ok) umma_commit(bar(ACC_FULL));
+      }
+      if (!ok) {  // nothing may still be running on TMEM when it is freed
+        umma_commit(bar(DRAIN));
+        (void)mbar_wait(bar(DRAIN), 0);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue = all-reduce
+    const int r = warp * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const int64_t ct = 32 * static_cast<int64_t>(bn);  // cells of one tile
+    const int64_t area1 = kHeaderBytes + (2 + static_cast<int64_t>(e & 1)) * p.stage_bytes;  // [tile slot][source][cell]
+    const int64_t area2 = kHeaderBytes + (6 + static_cast<int64_t>(e & 1)) * p.stage_bytes;  // [tile][cell]
+    bool gave_up = *s_broken != 0;
+    // a cell of this call, or (after the clock limit) whatever is there
+    auto wait_cell = [&](const uint4* src, uint4 v) {
+      if (!gave_up && (v.y != e || v.w != e)) {
+        const long long t0 = clock64();
+        do {
+          v = ld_volatile16(src);
+          if (clock64() - t0 > p.wait_cycles) {
+            atomicOr(p.status, NVLLM_STATUS_TIMEOUT);
+            *reinterpret_cast<volatile uint32_t*>(broken) = 1;
+            gave_up = true;
+            break;
+          }
+        } while (v.y != e || v.w != e);
+      }
+      return v;
+    };
+    auto store_row = [&](int t, int ch, const uint32_t (&res)[16]) {  // 32 columns of this thread's output row
+      const int mt = t / ntn, nt = t - mt * ntn;
+      uint4* dst = reinterpret_cast<uint4*>(p.out[mi] + static_cast<int64_t>(mt * BM + r) * p.out_stride + nt * bn + ch * 32);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) dst[q] = make_uint4(res[4 * q], res[4 * q + 1], res[4 * q + 2], res[4 * q + 3]);
+    };
+
+    int i = 0;
+    bool ok = true;
+    for (int t = b; t < tiles && ok; t += p.nblocks, ++i) {
+      const int mt = t / ntn;
+      const bool valid = mt * BM + r < p.m;
+      const int owner = t % w, slot = t / w;
+      if (!(ok = wait_or_abort(bar(ACC_FULL), i & 1, abort_flag))) break;
+      tc_fence_after();
+      for (int ch = 0; ch < bn / 32; ++ch) {
+        uint32_t v[32];
+        __syncwarp();  // lanes leave the previous chunk's cell waits at different times
+        tmem_ld32(tmem + lane_addr + ch * 32, v);
+        tmem_wait_ld();
+        if (ch == bn / 32 - 1) {  // the accumulator is in registers: the next tile may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(ACC_FREE));
+        }
+        uint32_t pk[16];  // this rank's partial, rounded to bf16 as the unfused projection would
+#pragma unroll
+        for (int q = 0; q < 16; ++q) pk[q] = pack_bf16x2(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]));
+        if (!valid) continue;
+        const int64_t idx0 = static_cast<int64_t>(ch * 8) * 128 + r;  // cell (column group ch*8 + cc, row r) = idx0 + cc * 128
+        if (owner != rank) {
+          uint4* dst = reinterpret_cast<uint4*>(p.peers.base[owner] + area1) + (static_cast<int64_t>(slot) * w + rank) * ct + idx0;
+#pragma unroll
+          for (int cc = 0; cc < 8; ++cc) st_volatile16(dst + cc * 128, make_uint4(pk[2 * cc], e, pk[2 * cc + 1], e));
+          continue;
+        }
+        // owner: partials in rank order; the next source's cells are in flight while one is added
+        float acc[8][4];
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) acc[cc][0] = acc[cc][1] = acc[cc][2] = acc[cc][3] = 0.f;
+        const uint4* mine = reinterpret_cast<const uint4*>(own + area1) + static_cast<int64_t>(slot) * w * ct + idx0;
+        uint4 cur[8], nxt[8];
+        auto fetch = [&](int src, uint4 (&buf)[8]) {
+          if (src >= w || src == rank) return;
+#pragma unroll
+          for (int cc = 0; cc < 8; ++cc) buf[cc] = ld_volatile16(mine + src * ct + cc * 128);
+        };
+        fetch(0, cur);
+        for (int src = 0; src < w; ++src) {
+          fetch(src + 1, nxt);
+          if (src == rank) {
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) add4(acc[cc], pk[2 * cc], pk[2 * cc + 1]);
+          } else {
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) {
+              const uint4 c = wait_cell(mine + src * ct + cc * 128, cur[cc]);
+              add4(acc[cc], c.x, c.z);
+            }
+          }
+#pragma unroll
+          for (int cc = 0; cc < 8; ++cc) cur[cc] = nxt[cc];
+        }
+        uint32_t res[16];
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+          res[2 * cc] = pack_bf16x2(acc[cc][0], acc[cc][1]);
+          res[2 * cc + 1] = pack_bf16x2(acc[cc][2], acc[cc][3]);
+        }
+        for (int k = 1; k < w; ++k) {
+          const int j = (rank + k) % w;  // every owner starts with another peer
+          uint4* dst = reinterpret_cast<uint4*>(p.peers.base[j] + area2) + static_cast<int64_t>(t) * ct + idx0;
+#pragma unroll
+          for (int cc = 0; cc < 8; ++cc) st_volatile16(dst + cc * 128, make_uint4(res[2 * cc], e, res[2 * cc + 1], e));
+        }
+        store_row(t, ch, res);
+      }
+    }
+    // the tiles that other ranks own arrive in this rank's result-cell area
+    for (int t = b; t < tiles && ok; t += p.nblocks) {
+      const int mt = t / ntn;
+      if (t % w == rank || mt * BM + r >= p.m) continue;
+      const uint4* results = reinterpret_cast<const uint4*>(own + area2) + static_cast<int64_t>(t) * ct + r;
+      for (int ch = 0; ch < bn / 32; ++ch) {
+        uint4 c[8];
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) c[cc] = ld_volatile16(results + (ch * 8 + cc) * 128);
+        uint32_t res[16];
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {
+          c[cc] = wait_cell(results + (ch * 8 + cc) * 128, c[cc]);
+          res[2 * cc] = c[cc].x;
+          res[2 * cc + 1] = c[cc].z;
+        }
+        store_row(t, ch, res);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (tid == 0) {
+    if (*abort_flag) atomicOr(p.status, NVLLM_STATUS_TIMEOUT);
+    epochs[b] = e;
+  }
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, tmem_cols);
+  }
+}
+
+// Tile width for a problem: the smallest of 32 / 64 / 128 columns that leaves at most one tile per
+// thread block (128 wide otherwise); 0 when the shape or the cell areas do not allow the kernel.
+static int pick_bn(int64_t m, int64_t n, int64_t k, int world, int64_t stage_bytes, int nblocks) {
+  if (m <= 0 || n <= 0 || k <= 0 || k % 8 || n % 32 || world < 2 || world > kMaxRanks) return 0;
+  const int64_t ntm = (m + BM - 1) / BM;
+  int bn = 0;
+  for (int c = 32; c <= 128; c *= 2) {
+    if (n % c) break;
+    bn = c;
+    if (ntm * (n / c) <= nblocks) break;
+  }
+  if (!bn) return 0;
+  const int64_t tiles = ntm * (n / bn), cell_bytes = 32 * static_cast<int64_t>(bn) * 16;
+  if (tiles < world) return 0;  // every rank must own a tile (the two-area argument needs a cell from every peer in every call)
+  if ((tiles + world - 1) / world * world * cell_bytes > stage_bytes) return 0;
+  if (tiles * cell_bytes > stage_bytes) return 0;
+  return bn;
+}
+
+static int prepare_kernel() {
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    (void)cudaGetLastError();
+    return fail(NVLLM_E_NO_DEVICE, "ar_gemm_allreduce: no CUDA device is usable");
+  }
+  if (!attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_allreduce_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      return fail(NVLLM_E_CUDA, "ar_gemm_allreduce: set-up failed: %s", cudaGetErrorString(e));
+    }
+    attr_done[dev] = true;
+  }
+  return NVLLM_OK;
+}
+
+}  // namespace gar
+}  // namespace nvllm
+
+using namespace nvllm;
+
+extern "C" int nvllm_ar_gemm_tile(int64_t m, int64_t n, int64_t k, int32_t world, int64_t max_bytes) {
+  return gar::pick_bn(m, n, k, world, max_bytes, ar::kGrid);
+}
+
+extern "C" int nvllm_ar_gemm_allreduce(const void* x, int64_t x_stride, const void* weight, int64_t w_stride, void* out,
+                                       int64_t out_stride, int64_t m, int64_t n, int64_t k, void* stream) {
+  ar::State* s = ar::current_state();
+  if (!s || !s->connected) return fail(NVLLM_E_GEOMETRY, "ar_gemm_allreduce: not connected (nvllm_ar_init + nvllm_ar_connect first)");
+  if (m == 0) return NVLLM_OK;
+  if (!x || !weight || !out) return fail(NVLLM_E_NULL, "ar_gemm_allreduce: NULL pointer argument");
+  if (!aligned16(x) || !aligned16(weight) || !aligned16(out) || x_stride % 8 || w_stride % 8 || out_stride % 8)
+    return fail(NVLLM_E_ALIGN, "ar_gemm_allreduce: pointers and row strides must be 16-byte aligned");
+  if (x_stride < k || w_stride < k || out_stride < n) return fail(NVLLM_E_GEOMETRY, "ar_gemm_allreduce: a row stride is shorter than its row");
+  const int bn = gar::pick_bn(m, n, k, s->world, s->stage_bytes, ar::kGrid);
+  if (!bn)
+    return fail(NVLLM_E_GEOMETRY, "ar_gemm_allreduce: m=%lld n=%lld k=%lld does not fit (n %% 32, k %% 8, at least one tile per rank, %lld-byte cell areas)",
+                (long long)m, (long long)n, (long long)k, (long long)s->stage_bytes);
+  if (int rc = gar::prepare_kernel()) return rc;
+  gar::Maps maps;
+  if (!sm100::make_tmap_3d(&maps.x[0], x, k, 1, m, k, x_stride, gar::BM)) return NVLLM_E_CUDA;
+  if (!sm100::make_tmap_3d(&maps.w[0], weight, k, 1, n, k, w_stride, bn)) return NVLLM_E_CUDA;
+  gar::Params p{};
+  p.out[0] = static_cast<__nv_bfloat16*>(out);
+  p.out_stride = out_stride;
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n);
+  p.k = static_cast<int>(k);
+  p.bn = bn;
+  p.rank = s->rank;
+  p.world = s->world;
+  p.nblocks = ar::kGrid;
+  p.stage_bytes = s->stage_bytes;
+  p.wait_cycles = s->wait_cycles;
+  p.peers = s->peers;
+  p.status = status_word();
+  if (!p.status) return fail(NVLLM_E_NO_DEVICE, "ar_gemm_allreduce: no CUDA device is usable");
+  gar::gemm_allreduce_kernel<<<ar::kGrid, gar::NTHREADS, gar::SMEM, static_cast<cudaStream_t>(stream)>>>(maps, p);
+  count_launch();
+  return check_launch("ar_gemm_allreduce launch");
+}
+
+extern "C" int nvllm_ar_gemm_allreduce_emulated(int32_t world, const void* const* xs, const void* const* weights, void* const* outputs,
+                                                int64_t m, int64_t n, int64_t k, void* scratch, int64_t scratch_bytes,
+                                                int64_t max_bytes, void* stream) {
+  if (world < 2 || world > ar::kMaxRanks) return fail(NVLLM_E_GEOMETRY, "ar_gemm_allreduce_emulated: world=%d invalid", world);
+  if (!xs || !weights || !outputs || !scratch) return fail(NVLLM_E_NULL, "ar_gemm_allreduce_emulated: NULL pointer argument");
+  if (max_bytes <= 0 || max_bytes % 16) return fail(NVLLM_E_GEOMETRY, "ar_gemm_allreduce_emulated: max_bytes invalid");
+  if (scratch_bytes < static_cast<int64_t>(world) * (ar::kHeaderBytes + ar::kAreas * max_bytes) || !aligned16(scratch))
+    return fail(NVLLM_E_WORKSPACE, "ar_gemm_allreduce_emulated: scratch too small or misaligned");
+  const int bn = gar::pick_bn(m, n, k, world, max_bytes, ar::kEmulatedGrid);
+  if (!bn) return fail(NVLLM_E_GEOMETRY, "ar_gemm_allreduce_emulated: m=%lld n=%lld k=%lld does not fit", (long long)m, (long long)n, (long long)k);
+  if (int rc = gar::prepare_kernel()) return rc;
+  gar::Maps maps;
+  gar::Params p{};
+  for (int r = 0; r < world; ++r) {
+    if (!xs[r] || !weights[r] || !outputs[r]) return fail(NVLLM_E_NULL, "ar_gemm_allreduce_emulated: NULL pointer argument");
+    if (!aligned16(xs[r]) || !aligned16(weights[r]) || !aligned16(outputs[r]))
+      return fail(NVLLM_E_ALIGN, "ar_gemm_allreduce_emulated: pointers must be 16-byte aligned");
+    if (!sm100::make_tmap_3d(&maps.x[r], xs[r], k, 1, m, k, k, gar::BM)) return NVLLM_E_CUDA;
+    if (!sm100::make_tmap_3d(&maps.w[r], weights[r], k, 1, n, k, k, bn)) return NVLLM_E_CUDA;
+    p.out[r] = static_cast<__nv_bfloat16*>(outputs[r]);
+    p.peers.base[r] = static_cast<unsigned char*>(scratch) + r * (ar::kHeaderBytes + ar::kAreas * max_bytes);
+  }
+  for (int r = world; r < ar::kMaxRanks; ++r) {
+    maps.x[r] = maps.x[0];
+    maps.w[r] = maps.w[0];
+  }
+  p.out_stride = n;
+  p.m = static_cast<int>(m);
+  p.n = static_cast<int>(n);
+  p.k = static_cast<int>(k);
+  p.bn = bn;
+  p.rank = -1;
+  p.world = world;
+  p.nblocks = ar::kEmulatedGrid;
+  p.stage_bytes = max_bytes;
+  p.wait_cycles = sm100::kWaitLimitCycles;
+  p.status = status_word();
+  if (!p.status) return fail(NVLLM_E_NO_DEVICE, "ar_gemm_allreduce_emulated: no CUDA device is usable");
+  // all ranks' blocks must be resident together (they wait on each other): a cooperative launch
+  // refuses to start otherwise
+  void* args[] = {&maps, &p};
+  cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(gar::gemm_allreduce_kernel), dim3(ar::kEmulatedGrid * world),
+                                              dim3(gar::NTHREADS), args, gar::SMEM, static_cast<cudaStream_t>(stream));
+  count_launch();
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(NVLLM_E_CUDA, "ar_gemm_allreduce_emulated launch: %s", cudaGetErrorString(e));
+  }
+  return NVLLM_OK;
+}

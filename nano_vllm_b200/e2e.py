@@ -79,16 +79,16 @@ def apply_shims(attn: str, ref_path: str):
         sys.path.insert(0, ref_path)
     if str(ROOT) not in sys.path:
         sys.path.insert(0, str(ROOT))
-    if attn in ("b200", "b200-fused", "b200-full", "b200-full-ar"):
+    if attn in ("b200", "b200-fused", "b200-full", "b200-full-ar", "b200-full-gemm-ar"):
         from nano_vllm_b200 import plugin
         plugin.install()
-        if attn in ("b200-fused", "b200-full", "b200-full-ar"):
+        if attn != "b200":
             plugin.fuse_pre_attention()
-        if attn in ("b200-full", "b200-full-ar"):
+        if attn in ("b200-full", "b200-full-ar", "b200-full-gemm-ar"):
             plugin.fuse_sampler()
             plugin.fuse_decode_inputs()
-        if attn == "b200-full-ar":
-            plugin.fuse_all_reduce()
+        if attn in ("b200-full-ar", "b200-full-gemm-ar"):
+            plugin.fuse_all_reduce(fuse_gemm=attn == "b200-full-gemm-ar")
             plugin.fuse_lm_head()
     import nanovllm.engine.model_runner as mr
     mr.load_model = random_init
@@ -140,10 +140,11 @@ def make_engine(model_dir: str, attn: str, ref_path: str, **kwargs):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--attn", default="b200", choices=["b200", "b200-fused", "b200-full", "b200-full-ar", "reference"],
+    ap.add_argument("--attn", default="b200", choices=["b200", "b200-fused", "b200-full", "b200-full-ar", "b200-full-gemm-ar", "reference"],
                     help="b200: swap the attention layer; b200-fused: also fuse q/k norm + rotary + store; "
                          "b200-full: also the one-pass sampler and the one-launch decode inputs; b200-full-ar: also the "
-                         "peer-memory all-reduce and the vocabulary-sharded sampling (TP > 1); reference: stock nano-vllm")
+                         "peer-memory all-reduce and the vocabulary-sharded sampling (TP > 1); b200-full-gemm-ar: also the "
+                         "row-parallel projections and their sums as one launch; reference: stock nano-vllm")
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--model", default="qwen3-0.6b", choices=sorted(GEOMETRY))
     ap.add_argument("--num-seqs", type=int, default=256)

@@ -178,7 +178,10 @@ def fuse_lm_head(seed: int = 0x5EED) -> None:
     mr.ModelRunner.call = call
 
 
-def fuse_all_reduce(max_bytes: int = 8 << 20, wait_ms: int = 60000) -> None:
+FUSED_GEMM_MAX_TOKENS = 512  # the decode graphs' largest batch (model_runner.py:306)
+
+
+def fuse_all_reduce(max_bytes: int = 8 << 20, wait_ms: int = 60000, fuse_gemm: bool = False) -> None:
     """Optional step for tensor-parallel runs: ``RowParallelLinear.forward``
     (nanovllm/layers/linear.py:195-199) sums its partial outputs with the peer-memory kernel
     (allreduce.PeerAllReduce) where that is expected to be the faster one (decode-sized tensors;
@@ -188,7 +191,9 @@ def fuse_all_reduce(max_bytes: int = 8 << 20, wait_ms: int = 60000) -> None:
     compiles or captures), hence the long default wait.  A wait that does run out leaves a latch
     in the kernel's buffers (later calls no longer wait and their sums are wrong) that only a
     shutdown clears; every 256th eager call (prefill steps) therefore reads the device status
-    word and raises if the time-out bit is set, instead of generating on."""
+    word and raises if the time-out bit is set, instead of generating on.  With ``fuse_gemm`` a
+    bias-free projection of a decode-sized batch runs as ONE launch that multiplies and sums
+    (PeerAllReduce.linear_all_reduce) where its shape allows."""
     import torch
     import torch.distributed as dist
     import torch.nn.functional as F
@@ -198,21 +203,25 @@ def fuse_all_reduce(max_bytes: int = 8 << 20, wait_ms: int = 60000) -> None:
     state = {"ar": None, "eager_calls": 0}
 
     def forward(self, x):
+        if self.tp_size == 1:
+            return F.linear(x, self.weight, self.bias)
+        ar = state["ar"]
+        capturing = torch.cuda.is_current_stream_capturing()
+        if ar is None and not capturing:
+            ar = state["ar"] = PeerAllReduce(dist.get_rank(), dist.get_world_size(), max_bytes, wait_ms=wait_ms)
+        if ar is not None and not capturing:
+            state["eager_calls"] += 1
+            if state["eager_calls"] % 256 == 0 and _lib.read_status() & 4:
+                raise RuntimeError("nano_vllm_b200: a peer all-reduce gave up waiting for another rank "
+                                   "(NVLLM_STATUS_TIMEOUT); the sums since then are invalid")
+        if (fuse_gemm and ar is not None and self.bias is None and x.dim() == 2 and x.shape[0] <= FUSED_GEMM_MAX_TOKENS
+                and ar.linear_fits(x, self.weight)):
+            return ar.linear_all_reduce(x, self.weight)
         y = F.linear(x, self.weight, self.bias if self.tp_rank == 0 else None)
-        if self.tp_size > 1:
-            ar = state["ar"]
-            capturing = torch.cuda.is_current_stream_capturing()
-            if ar is None and not capturing:
-                ar = state["ar"] = PeerAllReduce(dist.get_rank(), dist.get_world_size(), max_bytes, wait_ms=wait_ms)
-            if ar is not None and not capturing:
-                state["eager_calls"] += 1
-                if state["eager_calls"] % 256 == 0 and _lib.read_status() & 4:
-                    raise RuntimeError("nano_vllm_b200: a peer all-reduce gave up waiting for another rank "
-                                       "(NVLLM_STATUS_TIMEOUT); the sums since then are invalid")
-            if ar is not None and ar.preferred(y):
-                ar.all_reduce(y)
-            else:
-                dist.all_reduce(y)
+        if ar is not None and ar.preferred(y):
+            ar.all_reduce(y)
+        else:
+            dist.all_reduce(y)
         return y
 
     linear.RowParallelLinear.forward = forward

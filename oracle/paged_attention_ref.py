@@ -243,3 +243,11 @@ def allreduce_ref(inputs):
     for x in inputs:
         acc += x.to(torch.float32)
     return acc.to(torch.bfloat16)
+
+
+def row_parallel_linear_ref(xs, weights):
+    """RowParallelLinear.forward over all ranks (nanovllm/layers/linear.py:195-199, no bias):
+    every rank's F.linear in fp32 rounded to bf16 (what the rank's GEMM returns), then the sum of
+    those partials as ``allreduce_ref`` forms it."""
+    partials = [(x.to(torch.float32) @ w.to(torch.float32).t()).to(torch.bfloat16) for x, w in zip(xs, weights)]
+    return allreduce_ref(partials)
