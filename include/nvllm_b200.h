@@ -346,7 +346,8 @@ NVLLM_API int nvllm_ar_allreduce_emulated(int32_t world, const void* const* inpu
  * and its epilogue sums the partials over peer memory tile by tile -- each rank's fp32 partial is
  * rounded to bf16 (as F.linear would have), a tile's partials go to the tile's owner rank as
  * flagged cells, the owner adds them in rank order in fp32, rounds once and sends the result to
- * every rank, so all ranks hold the same bits.  Needs nvllm_ar_init + nvllm_ar_connect; every rank
+ * every rank (two shots), or -- at two ranks and for small outputs -- go to every rank, which adds
+ * them in rank order itself (one shot); either way all ranks hold the same bits.  Needs nvllm_ar_init + nvllm_ar_connect; every rank
  * makes the same calls in the same order, and calls may be mixed freely with nvllm_ar_allreduce.
  * x, weight, out: 16-byte aligned, row strides (elements) multiples of 8; k a multiple of 8, n of 32.
  * nvllm_ar_gemm_tile() returns the tile width (32, 64 or 128) the call would use, or 0 when the
@@ -358,10 +359,11 @@ NVLLM_API int nvllm_ar_gemm_allreduce(const void* x, int64_t x_stride, const voi
                             int64_t out_stride, int64_t m, int64_t n, int64_t k, void* stream);
 /* The same with all ranks emulated by ONE cooperative launch on the current device (xs[r] [m, k],
  * weights[r] [n, k], outputs[r] [m, n], all contiguous; scratch as for nvllm_ar_allreduce_emulated).
- * No counterpart in the reference. */
+ * mode: 0 = the kernel's own choice between one and two shots, 1 = one shot where the cell areas
+ * hold it, 2 = two shots.  No counterpart in the reference. */
 NVLLM_API int nvllm_ar_gemm_allreduce_emulated(int32_t world, const void* const* xs, const void* const* weights,
                                      void* const* outputs, int64_t m, int64_t n, int64_t k, void* scratch,
-                                     int64_t scratch_bytes, int64_t max_bytes, void* stream);
+                                     int64_t scratch_bytes, int64_t max_bytes, int32_t mode, void* stream);
 
 /* Known-answer check of the tensor-core building blocks the prefill kernel is made of
  * (TMA swizzled loads, shared-memory and instruction descriptors, TMEM loads and stores):

@@ -58,7 +58,7 @@ SIGNATURES = {
     "nvllm_ar_gemm_allreduce": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64,
                                           c_int64, c_void_p]),
     "nvllm_ar_gemm_allreduce_emulated": (c_int32, [c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
-                                                   c_void_p, c_int64, c_int64, c_void_p]),
+                                                   c_void_p, c_int64, c_int64, c_int32, c_void_p]),
     "nvllm_selftest_umma": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "nvllm_selftest_wait_expiry": (c_int32, [c_void_p, c_void_p]),
     "nvllm_last_error": (c_char_p, []),

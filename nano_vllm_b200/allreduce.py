@@ -130,10 +130,11 @@ def all_reduce_emulated(inputs: list[torch.Tensor], scratch: torch.Tensor, max_b
 
 
 def linear_all_reduce_emulated(xs: list[torch.Tensor], weights: list[torch.Tensor], scratch: torch.Tensor,
-                               max_bytes: int) -> list[torch.Tensor]:
+                               max_bytes: int, mode: int = 0) -> list[torch.Tensor]:
     """The fused projection + all-reduce of every rank in one cooperative launch on one device
     (test aid): ``xs[r]`` [m, k], ``weights[r]`` [n, k] contiguous; returns one [m, n] output per
-    rank.  ``scratch`` as for ``all_reduce_emulated`` (the two may share it)."""
+    rank.  ``scratch`` as for ``all_reduce_emulated`` (the two may share it).  ``mode``: 0 the
+    kernel's choice, 1 one shot (every rank sums every tile), 2 two shots (a tile's owner sums)."""
     world = len(xs)
     m, k = xs[0].shape
     n = weights[0].shape[0]
@@ -142,6 +143,6 @@ def linear_all_reduce_emulated(xs: list[torch.Tensor], weights: list[torch.Tenso
     with torch.cuda.device(xs[0].device):
         _lib.check(_lib.load().nvllm_ar_gemm_allreduce_emulated(
             world, arr(*[x.data_ptr() for x in xs]), arr(*[w.data_ptr() for w in weights]),
-            arr(*[o.data_ptr() for o in outs]), m, n, k, scratch.data_ptr(), scratch.numel(), max_bytes,
+            arr(*[o.data_ptr() for o in outs]), m, n, k, scratch.data_ptr(), scratch.numel(), max_bytes, mode,
             torch.cuda.current_stream(xs[0].device).cuda_stream))
     return outs

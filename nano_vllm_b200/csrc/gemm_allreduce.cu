@@ -26,6 +26,8 @@
 // 16-byte stores issued by each thread; TMA loads read this rank's own X and W.
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+
 #include "allreduce.cuh"
 #include "prefill_tc.cuh"
 
@@ -34,13 +36,19 @@ namespace gar {
 using namespace sm100;
 using namespace ar;
 
-constexpr int BM = 128, BK = 64, NST = 6, NTHREADS = 192;
-constexpr int A_BYTES = BM * BK * 2;        // 16 KB: one 128-byte-swizzled [128 x 64] sub-tile
-constexpr int STAGE_BYTES = 2 * A_BYTES;    // X tile + room for a W tile of up to 128 rows
-constexpr int OFF_CTRL = NST * STAGE_BYTES;
-constexpr int SMEM = OFF_CTRL + 256 + 1024;  // + barriers, misc + alignment slack
-enum Bar { FULL0 = 0, EMPTY0 = NST, ACC_FULL = 2 * NST, ACC_FREE, DRAIN, NUM_BARS };
-static_assert(NUM_BARS * 8 <= 192, "barrier area");
+constexpr int BM = 128, BK = 64, NTHREADS = 192;
+// Shared memory: [control 1 KB | ring | 16 KB that only the products' unused rows reach].  A stage
+// holds a_rows x 64 elements of X and bn x 64 of W as 128-byte-swizzled rows; a_rows is the batch
+// rounded up to 16 (128 when there are several row tiles).  The product always reads 128 rows of
+// X from the stage's start: for a small batch the rows past a_rows are whatever follows in the
+// ring (the W tile, later stages).  An output row depends on its own X row only, so that garbage
+// ends in accumulator rows nobody reads, and the ring holds far more k-blocks in flight -- with a
+// batch of 16 a stage is 6 KB instead of 20, 24 stages deep instead of 6.
+constexpr int MAX_NST = 24;
+constexpr int CTRL_BYTES = 1024, RING_BYTES = 192 * 1024, SLACK_BYTES = BM * 128;
+constexpr int SMEM = CTRL_BYTES + RING_BYTES + SLACK_BYTES + 1024;  // + alignment slack
+enum Bar { FULL0 = 0, EMPTY0 = MAX_NST, ACC_FULL = 2 * MAX_NST, ACC_FREE, DRAIN, NUM_BARS };
+static_assert(NUM_BARS * 8 <= 512, "barrier area");
 
 struct Maps {
   CUtensorMap x[kMaxRanks];  // [m, k] activations of each rank (one entry unless emulated)
@@ -51,6 +59,9 @@ struct Params {
   __nv_bfloat16* out[kMaxRanks];
   int64_t out_stride;  // elements between output rows
   int m, n, k, bn;
+  int a_rows;          // rows of X per stage (box height of the X tensor map)
+  int nst;             // stages in the ring
+  int one_shot;        // every rank sums every tile itself (one NVLink crossing) instead of the tile's owner
   int rank;            // >= 0: this process's rank; < 0: emulated, rank = blockIdx.x / nblocks
   int world, nblocks;  // thread blocks per rank
   int64_t stage_bytes;
@@ -69,12 +80,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_allreduce_kernel(const __gri
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t bars = base + OFF_CTRL;
+  const uint32_t bars = base;
   auto bar = [&](int i) { return bars + 8u * i; };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + OFF_CTRL + 192);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + OFF_CTRL + 200);
-  volatile uint32_t* s_epoch = reinterpret_cast<volatile uint32_t*>(base_ptr + OFF_CTRL + 204);
-  volatile int* s_broken = reinterpret_cast<volatile int*>(base_ptr + OFF_CTRL + 208);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + 512);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + 520);
+  volatile uint32_t* s_epoch = reinterpret_cast<volatile uint32_t*>(base_ptr + 524);
+  volatile int* s_broken = reinterpret_cast<volatile int*>(base_ptr + 528);
+  const uint32_t ring = base + CTRL_BYTES;
+  const int NST = p.nst, a_bytes = p.a_rows * 128, stage_bytes = a_bytes + bn * 128;
 
   unsigned char* own = p.peers.base[rank];
   uint32_t* epochs = reinterpret_cast<uint32_t*>(own + kCellEpochOff);
@@ -115,9 +128,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_allreduce_kernel(const __gri
         for (int kb = 0; kb < nkb; ++kb, ++g) {
           const int s = g % NST, use = g / NST;
           if (use > 0 && !(ok = wait_or_abort(bar(EMPTY0 + s), (use - 1) & 1, abort_flag))) break;
-          mbar_expect_tx(bar(FULL0 + s), A_BYTES + bn * 128);
-          tma_load_3d(base + s * STAGE_BYTES, &maps.x[mi], bar(FULL0 + s), kb * BK, 0, mt * BM);
-          tma_load_3d(base + s * STAGE_BYTES + A_BYTES, &maps.w[mi], bar(FULL0 + s), kb * BK, 0, nt * bn);
+          mbar_expect_tx(bar(FULL0 + s), stage_bytes);
+          tma_load_3d(ring + s * stage_bytes, &maps.x[mi], bar(FULL0 + s), kb * BK, 0, mt * BM);
+          tma_load_3d(ring + s * stage_bytes + a_bytes, &maps.w[mi], bar(FULL0 + s), kb * BK, 0, nt * bn);
         }
       }
     }
@@ -135,7 +148,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_allreduce_kernel(const __gri
           const int s = g % NST, use = g / NST;
           if (!(ok = wait_or_abort(bar(FULL0 + s), use & 1, abort_flag))) break;
           tc_fence_after();
-          const uint32_t a = base + s * STAGE_BYTES, bsm = a + A_BYTES;
+          const uint32_t a = ring + s * stage_bytes, bsm = a + a_bytes;
 #pragma unroll
           for (int ks = 0; ks < BK / 16; ++ks)
             umma_ss(tmem, umma_desc(a + ks * 32, 16, 1024), umma_desc(bsm + ks * 32, 16, 1024), idesc, (kb > 0 || ks > 0) ? 1u : 0u);
@@ -184,7 +197,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_allreduce_kernel(const __gri
     for (int t = b; t < tiles && ok; t += p.nblocks, ++i) {
       const int mt = t / ntn;
       const bool valid = mt * BM + r < p.m;
-      const int owner = t % w, slot = t / w;
+      const int owner = p.one_shot ? rank : t % w, slot = p.one_shot ? t : t / w;
       if (!(ok = wait_or_abort(bar(ACC_FULL), i & 1, abort_flag))) break;
       tc_fence_after();
       for (int ch = 0; ch < bn / 32; ++ch) {
@@ -207,6 +220,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_allreduce_kernel(const __gri
 #pragma unroll
           for (int cc = 0; cc < 8; ++cc) st_volatile16(dst + cc * 128, make_uint4(pk[2 * cc], e, pk[2 * cc + 1], e));
           continue;
+        }
+        if (p.one_shot) {  // every rank sums: my partial goes to every peer
+          for (int k = 1; k < w; ++k) {
+            const int j = (rank + k) % w;
+            uint4* dst = reinterpret_cast<uint4*>(p.peers.base[j] + area1) + (static_cast<int64_t>(slot) * w + rank) * ct + idx0;
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) st_volatile16(dst + cc * 128, make_uint4(pk[2 * cc], e, pk[2 * cc + 1], e));
+          }
         }
         // owner: partials in rank order; the next source's cells are in flight while one is added
         float acc[8][4];
@@ -241,7 +262,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_allreduce_kernel(const __gri
           res[2 * cc] = pack_bf16x2(acc[cc][0], acc[cc][1]);
           res[2 * cc + 1] = pack_bf16x2(acc[cc][2], acc[cc][3]);
         }
-        for (int k = 1; k < w; ++k) {
+        for (int k = 1; k < w && !p.one_shot; ++k) {
           const int j = (rank + k) % w;  // every owner starts with another peer
           uint4* dst = reinterpret_cast<uint4*>(p.peers.base[j] + area2) + static_cast<int64_t>(t) * ct + idx0;
 #pragma unroll
@@ -251,7 +272,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_allreduce_kernel(const __gri
       }
     }
     // the tiles that other ranks own arrive in this rank's result-cell area
-    for (int t = b; t < tiles && ok; t += p.nblocks) {
+    for (int t = b; t < tiles && ok && !p.one_shot; t += p.nblocks) {
       const int mt = t / ntn;
       if (t % w == rank || mt * BM + r >= p.m) continue;
       const uint4* results = reinterpret_cast<const uint4*>(own + area2) + static_cast<int64_t>(t) * ct + r;
@@ -283,10 +304,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_allreduce_kernel(const __gri
   }
 }
 
-// Tile width for a problem: the smallest of 32 / 64 / 128 columns that leaves at most one tile per
-// thread block (128 wide otherwise); 0 when the shape or the cell areas do not allow the kernel.
-static int pick_bn(int64_t m, int64_t n, int64_t k, int world, int64_t stage_bytes, int nblocks) {
-  if (m <= 0 || n <= 0 || k <= 0 || k % 8 || n % 32 || world < 2 || world > kMaxRanks) return 0;
+// How a problem is run.  bn: the smallest of 32 / 64 / 128 columns that leaves at most one tile per
+// thread block (128 wide otherwise).  one_shot: every rank pushes its partial of every tile to
+// every peer and sums for itself -- one NVLink crossing instead of two, (w-1) x the bytes; chosen
+// by the rule of the plain all-reduce (always at two ranks, at more while the extra bytes stay
+// under kCellsOneShotExtraBytes) where the cell area holds a region per tile and source.
+// mode: 0 = that rule, 1 = one shot where it fits, 2 = two shots.  bn == 0: the shape or the cell
+// areas do not allow the kernel.
+struct Plan {
+  int bn = 0, a_rows = 0, nst = 0, one_shot = 0;
+};
+static Plan make_plan(int64_t m, int64_t n, int64_t k, int world, int64_t stage_bytes, int nblocks, int mode) {
+  Plan pl;
+  if (m <= 0 || n <= 0 || k <= 0 || k % 8 || n % 32 || world < 2 || world > kMaxRanks) return pl;
   const int64_t ntm = (m + BM - 1) / BM;
   int bn = 0;
   for (int c = 32; c <= 128; c *= 2) {
@@ -294,12 +324,25 @@ static int pick_bn(int64_t m, int64_t n, int64_t k, int world, int64_t stage_byt
     bn = c;
     if (ntm * (n / c) <= nblocks) break;
   }
-  if (!bn) return 0;
+  if (!bn) return pl;
   const int64_t tiles = ntm * (n / bn), cell_bytes = 32 * static_cast<int64_t>(bn) * 16;
-  if (tiles < world) return 0;  // every rank must own a tile (the two-area argument needs a cell from every peer in every call)
-  if ((tiles + world - 1) / world * world * cell_bytes > stage_bytes) return 0;
-  if (tiles * cell_bytes > stage_bytes) return 0;
-  return bn;
+  const bool one_fits = tiles * world * cell_bytes <= stage_bytes;
+  // two shots: every rank must own a tile (the two-area argument needs a cell from every peer in every call)
+  const bool two_fits = tiles >= world && (tiles + world - 1) / world * world * cell_bytes <= stage_bytes &&
+                        tiles * cell_bytes <= stage_bytes;
+  const bool one_preferred = world == 2 || m * n * 2 * (world - 1) * (2 * world - 4) / world <= kCellsOneShotExtraBytes;
+  if (one_fits && (mode == 1 || (mode == 0 && one_preferred) || !two_fits)) pl.one_shot = 1;
+  else if (!two_fits) return pl;
+  pl.bn = bn;
+  pl.a_rows = ntm > 1 ? BM : static_cast<int>((m + 15) / 16 * 16);
+  const int stage = (pl.a_rows + bn) * 128;
+  pl.nst = RING_BYTES / stage < MAX_NST ? RING_BYTES / stage : MAX_NST;
+  return pl;
+}
+static int mode_from_env() {  // measurement aid, read on every call; the same on every rank
+  const char* s = std::getenv("NVLLM_GEMM_AR_MODE");
+  const int v = s ? std::atoi(s) : 0;
+  return v >= 0 && v <= 2 ? v : 0;
 }
 
 static int prepare_kernel() {
@@ -326,7 +369,7 @@ static int prepare_kernel() {
 using namespace nvllm;
 
 extern "C" int nvllm_ar_gemm_tile(int64_t m, int64_t n, int64_t k, int32_t world, int64_t max_bytes) {
-  return gar::pick_bn(m, n, k, world, max_bytes, ar::kGrid);
+  return gar::make_plan(m, n, k, world, max_bytes, ar::kGrid, gar::mode_from_env()).bn;
 }
 
 extern "C" int nvllm_ar_gemm_allreduce(const void* x, int64_t x_stride, const void* weight, int64_t w_stride, void* out,
@@ -338,13 +381,14 @@ extern "C" int nvllm_ar_gemm_allreduce(const void* x, int64_t x_stride, const vo
   if (!aligned16(x) || !aligned16(weight) || !aligned16(out) || x_stride % 8 || w_stride % 8 || out_stride % 8)
     return fail(NVLLM_E_ALIGN, "ar_gemm_allreduce: pointers and row strides must be 16-byte aligned");
   if (x_stride < k || w_stride < k || out_stride < n) return fail(NVLLM_E_GEOMETRY, "ar_gemm_allreduce: a row stride is shorter than its row");
-  const int bn = gar::pick_bn(m, n, k, s->world, s->stage_bytes, ar::kGrid);
+  const gar::Plan pl = gar::make_plan(m, n, k, s->world, s->stage_bytes, ar::kGrid, gar::mode_from_env());
+  const int bn = pl.bn;
   if (!bn)
     return fail(NVLLM_E_GEOMETRY, "ar_gemm_allreduce: m=%lld n=%lld k=%lld does not fit (n %% 32, k %% 8, at least one tile per rank, %lld-byte cell areas)",
                 (long long)m, (long long)n, (long long)k, (long long)s->stage_bytes);
   if (int rc = gar::prepare_kernel()) return rc;
   gar::Maps maps;
-  if (!sm100::make_tmap_3d(&maps.x[0], x, k, 1, m, k, x_stride, gar::BM)) return NVLLM_E_CUDA;
+  if (!sm100::make_tmap_3d(&maps.x[0], x, k, 1, m, k, x_stride, pl.a_rows)) return NVLLM_E_CUDA;
   if (!sm100::make_tmap_3d(&maps.w[0], weight, k, 1, n, k, w_stride, bn)) return NVLLM_E_CUDA;
   gar::Params p{};
   p.out[0] = static_cast<__nv_bfloat16*>(out);
@@ -353,6 +397,9 @@ extern "C" int nvllm_ar_gemm_allreduce(const void* x, int64_t x_stride, const vo
   p.n = static_cast<int>(n);
   p.k = static_cast<int>(k);
   p.bn = bn;
+  p.a_rows = pl.a_rows;
+  p.nst = pl.nst;
+  p.one_shot = pl.one_shot;
   p.rank = s->rank;
   p.world = s->world;
   p.nblocks = ar::kGrid;
@@ -368,13 +415,15 @@ extern "C" int nvllm_ar_gemm_allreduce(const void* x, int64_t x_stride, const vo
 
 extern "C" int nvllm_ar_gemm_allreduce_emulated(int32_t world, const void* const* xs, const void* const* weights, void* const* outputs,
                                                 int64_t m, int64_t n, int64_t k, void* scratch, int64_t scratch_bytes,
-                                                int64_t max_bytes, void* stream) {
+                                                int64_t max_bytes, int32_t mode, void* stream) {
   if (world < 2 || world > ar::kMaxRanks) return fail(NVLLM_E_GEOMETRY, "ar_gemm_allreduce_emulated: world=%d invalid", world);
   if (!xs || !weights || !outputs || !scratch) return fail(NVLLM_E_NULL, "ar_gemm_allreduce_emulated: NULL pointer argument");
   if (max_bytes <= 0 || max_bytes % 16) return fail(NVLLM_E_GEOMETRY, "ar_gemm_allreduce_emulated: max_bytes invalid");
   if (scratch_bytes < static_cast<int64_t>(world) * (ar::kHeaderBytes + ar::kAreas * max_bytes) || !aligned16(scratch))
     return fail(NVLLM_E_WORKSPACE, "ar_gemm_allreduce_emulated: scratch too small or misaligned");
-  const int bn = gar::pick_bn(m, n, k, world, max_bytes, ar::kEmulatedGrid);
+  if (mode < 0 || mode > 2) return fail(NVLLM_E_GEOMETRY, "ar_gemm_allreduce_emulated: mode=%d invalid", mode);
+  const gar::Plan pl = gar::make_plan(m, n, k, world, max_bytes, ar::kEmulatedGrid, mode);
+  const int bn = pl.bn;
   if (!bn) return fail(NVLLM_E_GEOMETRY, "ar_gemm_allreduce_emulated: m=%lld n=%lld k=%lld does not fit", (long long)m, (long long)n, (long long)k);
   if (int rc = gar::prepare_kernel()) return rc;
   gar::Maps maps;
@@ -383,7 +432,7 @@ extern "C" int nvllm_ar_gemm_allreduce_emulated(int32_t world, const void* const
     if (!xs[r] || !weights[r] || !outputs[r]) return fail(NVLLM_E_NULL, "ar_gemm_allreduce_emulated: NULL pointer argument");
     if (!aligned16(xs[r]) || !aligned16(weights[r]) || !aligned16(outputs[r]))
       return fail(NVLLM_E_ALIGN, "ar_gemm_allreduce_emulated: pointers must be 16-byte aligned");
-    if (!sm100::make_tmap_3d(&maps.x[r], xs[r], k, 1, m, k, k, gar::BM)) return NVLLM_E_CUDA;
+    if (!sm100::make_tmap_3d(&maps.x[r], xs[r], k, 1, m, k, k, pl.a_rows)) return NVLLM_E_CUDA;
     if (!sm100::make_tmap_3d(&maps.w[r], weights[r], k, 1, n, k, k, bn)) return NVLLM_E_CUDA;
     p.out[r] = static_cast<__nv_bfloat16*>(outputs[r]);
     p.peers.base[r] = static_cast<unsigned char*>(scratch) + r * (ar::kHeaderBytes + ar::kAreas * max_bytes);
@@ -397,6 +446,9 @@ extern "C" int nvllm_ar_gemm_allreduce_emulated(int32_t world, const void* const
   p.n = static_cast<int>(n);
   p.k = static_cast<int>(k);
   p.bn = bn;
+  p.a_rows = pl.a_rows;
+  p.nst = pl.nst;
+  p.one_shot = pl.one_shot;
   p.rank = -1;
   p.world = world;
   p.nblocks = ar::kEmulatedGrid;

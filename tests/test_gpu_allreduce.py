@@ -138,6 +138,30 @@ for _ in range(4):
     g.replay()
     torch.cuda.synchronize()
     ok = ok and bool((y == world ** 3).all())
+# the projection fused with its sum, between plain calls and from a graph (integer operands: exact)
+def ints(shape, seed):
+    gen = torch.Generator().manual_seed(seed)
+    return (torch.randint(-1, 2, shape, generator=gen) * (torch.rand(shape, generator=gen) < 0.25)).to(torch.bfloat16)
+for i, (m, n, k) in enumerate([(8, 1024, 256), (200, 1024, 320), (256, 4096, 512)]):
+    xs = [ints((m, k), 10 * i + r) for r in range(world)]
+    ws = [ints((n, k), 10 * i + 5 + r) for r in range(world)]
+    want = R.row_parallel_linear_ref(xs, ws)
+    x, w = xs[rank].cuda(), ws[rank].cuda()
+    out = ar.linear_all_reduce(x, w)
+    t = torch.ones(64, dtype=torch.bfloat16, device="cuda")
+    ar.all_reduce(t)
+    torch.cuda.synchronize()
+    ok = ok and torch.equal(out.cpu().view(torch.int16), want.view(torch.int16)) and bool((t == world).all())
+g2 = torch.cuda.CUDAGraph()
+with torch.cuda.stream(s):
+    with torch.cuda.graph(g2, stream=s):
+        for _ in range(3):
+            ar.linear_all_reduce(x, w, out)
+for _ in range(4):
+    out.zero_()
+    g2.replay()
+    torch.cuda.synchronize()
+    ok = ok and torch.equal(out.cpu().view(torch.int16), want.view(torch.int16))
 status = _lib.read_status()
 dist.barrier()
 ar.close()

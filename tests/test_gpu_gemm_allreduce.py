@@ -23,12 +23,16 @@ def _small_ints(shape, g, density):
     return (v * keep).to(torch.bfloat16)
 
 
+@pytest.mark.parametrize("mode", [1, 2])
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("m,n,k", [(8, 256, 128), (200, 1024, 320), (128, 4096, 512), (1, 1024, 64), (256, 2048, 1536)])
-def test_emulated_ranks_exact_on_integer_operands(cuda, world, m, n, k):
-    """Operands in {-1, 0, 1}: no rounding anywhere, so every rank must hold the oracle's bits.
-    Shapes: one ragged row tile; two row tiles with k not a multiple of the 64-element k-block;
-    more tiles than thread blocks (a block loops); a single row; a long k (the stage ring wraps)."""
+@pytest.mark.parametrize("m,n,k", [(8, 256, 128), (200, 1024, 320), (128, 4096, 512), (1, 1024, 64), (40, 512, 6144),
+                                   (256, 2048, 1536)])
+def test_emulated_ranks_exact_on_integer_operands(cuda, world, m, n, k, mode):
+    """Operands in {-1, 0, 1}: no rounding anywhere, so every rank must hold the oracle's bits, in
+    one shot (every rank sums every tile; falls back to two where the cell areas are too small) and
+    in two (the tile's owner sums).  Shapes: one ragged row tile; two row tiles with k not a multiple
+    of the 64-element k-block; more tiles than thread blocks (a block loops); a single row; a small
+    batch with a long k (short stages, the deep ring wraps); two full row tiles."""
     g = torch.Generator().manual_seed(1000 * world + m)
     xs = [_small_ints((m, k), g, 0.25) for _ in range(world)]
     ws = [_small_ints((n, k), g, 0.25) for _ in range(world)]
@@ -36,7 +40,7 @@ def test_emulated_ranks_exact_on_integer_operands(cuda, world, m, n, k):
     assert want.abs().max() <= 256  # integers up to 256 are exact in bf16
     scratch = _scratch(cuda, world)
     for _ in range(3):  # the two cell areas alternate; the third call reuses the first
-        outs = AR.linear_all_reduce_emulated([x.to(cuda) for x in xs], [w.to(cuda) for w in ws], scratch, MAX_BYTES)
+        outs = AR.linear_all_reduce_emulated([x.to(cuda) for x in xs], [w.to(cuda) for w in ws], scratch, MAX_BYTES, mode)
         torch.cuda.synchronize()
         for r, o in enumerate(outs):
             assert torch.equal(o.cpu().view(torch.int16), want.view(torch.int16)), f"rank {r}"
@@ -73,7 +77,8 @@ def test_emulated_fused_and_plain_calls_share_the_cell_areas(cuda):
         if step % 2 == 0:
             xs = [_small_ints((64, 256), g, 0.25) for _ in range(world)]
             ws = [_small_ints((512, 256), g, 0.25) for _ in range(world)]
-            outs = AR.linear_all_reduce_emulated([x.to(cuda) for x in xs], [w.to(cuda) for w in ws], scratch, MAX_BYTES)
+            outs = AR.linear_all_reduce_emulated([x.to(cuda) for x in xs], [w.to(cuda) for w in ws], scratch, MAX_BYTES,
+                                                 mode=1 + step // 2 % 2)
             want = R.row_parallel_linear_ref(xs, ws)
         else:
             xs = [(torch.randn(64 * 512, generator=g) * 2).to(torch.bfloat16) for _ in range(world)]
@@ -92,7 +97,7 @@ def test_shapes_the_kernel_refuses(cuda):
     assert lib.nvllm_ar_gemm_tile(1024, 4096, 512, 8, 8 << 20) == 0   # cell areas too small
     assert lib.nvllm_ar_gemm_tile(8, 4096, 100, 2, 8 << 20) == 0      # k not a multiple of 8
     assert lib.nvllm_ar_gemm_tile(8, 48, 64, 2, 8 << 20) == 0         # n not a multiple of 32
-    assert lib.nvllm_ar_gemm_tile(8, 64, 64, 4, 8 << 20) == 0         # fewer tiles than ranks
+    assert lib.nvllm_ar_gemm_tile(8, 64, 64, 4, 8 << 20) == 32        # fewer tiles than ranks: one shot
     x = torch.zeros(8, 64, dtype=torch.bfloat16, device=cuda)
     w = torch.zeros(48, 64, dtype=torch.bfloat16, device=cuda)
     with pytest.raises(RuntimeError):
