@@ -42,8 +42,9 @@ constexpr int BM = 128, BK = 64, NTHREADS = 192;
 // rounded up to 16 (128 when there are several row tiles).  The product always reads 128 rows of
 // X from the stage's start: for a small batch the rows past a_rows are whatever follows in the
 // ring (the W tile, later stages).  An output row depends on its own X row only, so that garbage
-// ends in accumulator rows nobody reads, and the ring holds far more k-blocks in flight -- with a
-// batch of 16 a stage is 6 KB instead of 20, 24 stages deep instead of 6.
+// ends in accumulator rows nobody reads, and a small batch's stages hold far more of k.  A stage
+// covers ksub = 4, 2 or 1 k-blocks of 64 elements (one barrier round trip and one commit per
+// stage: with one k-block per stage the issuing threads, not the memory system, set the pace).
 constexpr int MAX_NST = 24;
 constexpr int CTRL_BYTES = 1024, RING_BYTES = 192 * 1024, SLACK_BYTES = BM * 128;
 constexpr int SMEM = CTRL_BYTES + RING_BYTES + SLACK_BYTES + 1024;  // + alignment slack
@@ -60,6 +61,7 @@ struct Params {
   int64_t out_stride;  // elements between output rows
   int m, n, k, bn;
   int a_rows;          // rows of X per stage (box height of the X tensor map)
+  int ksub;            // 64-element k-blocks per stage (one barrier round trip and one commit per stage)
   int nst;             // stages in the ring
   int one_shot;        // every rank sums every tile itself (one NVLink crossing) instead of the tile's owner
   int rank;            // >= 0: this process's rank; < 0: emulated, rank = blockIdx.x / nblocks
@@ -87,7 +89,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_allreduce_kernel(const __gri
   volatile uint32_t* s_epoch = reinterpret_cast<volatile uint32_t*>(base_ptr + 524);
   volatile int* s_broken = reinterpret_cast<volatile int*>(base_ptr + 528);
   const uint32_t ring = base + CTRL_BYTES;
-  const int NST = p.nst, a_bytes = p.a_rows * 128, stage_bytes = a_bytes + bn * 128;
+  // a stage = ksub sub-tiles of 64 k-elements, each [X rows | W rows] x 128 B
+  const int NST = p.nst, ksub = p.ksub, a_bytes = p.a_rows * 128, sub_bytes = a_bytes + bn * 128, stage_bytes = ksub * sub_bytes;
 
   unsigned char* own = p.peers.base[rank];
   uint32_t* epochs = reinterpret_cast<uint32_t*>(own + kCellEpochOff);
@@ -121,16 +124,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_allreduce_kernel(const __gri
   if (warp == 4) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int g = 0;  // k-blocks loaded so far in this block's life
+      int s = 0, use = 0;  // ring position: stage and how often it has been used
       bool ok = true;
       for (int t = b; t < tiles && ok; t += p.nblocks) {
         const int mt = t / ntn, nt = t - mt * ntn;
-        for (int kb = 0; kb < nkb; ++kb, ++g) {
-          const int s = g % NST, use = g / NST;
+        for (int kb = 0; kb < nkb; kb += ksub) {
           if (use > 0 && !(ok = wait_or_abort(bar(EMPTY0 + s), (use - 1) & 1, abort_flag))) break;
+          // every sub-tile is fetched, also past the end of k: those arrive as zeros and add nothing
           mbar_expect_tx(bar(FULL0 + s), stage_bytes);
-          tma_load_3d(ring + s * stage_bytes, &maps.x[mi], bar(FULL0 + s), kb * BK, 0, mt * BM);
-          tma_load_3d(ring + s * stage_bytes + a_bytes, &maps.w[mi], bar(FULL0 + s), kb * BK, 0, nt * bn);
+          const uint32_t dst = ring + s * stage_bytes;
+          for (int j = 0; j < ksub; ++j) {
+            tma_load_3d(dst + j * sub_bytes, &maps.x[mi], bar(FULL0 + s), (kb + j) * BK, 0, mt * BM);
+            tma_load_3d(dst + j * sub_bytes + a_bytes, &maps.w[mi], bar(FULL0 + s), (kb + j) * BK, 0, nt * bn);
+          }
+          if (++s == NST) {
+            s = 0;
+            ++use;
+          }
         }
       }
     }
@@ -138,21 +148,29 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_allreduce_kernel(const __gri
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma_idesc(BM, bn, 0, 0);
-      int g = 0, i = 0;
+      const uint64_t desc0 = umma_desc(ring, 16, 1024);
+      int s = 0, use = 0, i = 0;
       bool ok = true;
       for (int t = b; t < tiles && ok; t += p.nblocks, ++i) {
         // the accumulator is overwritten: the previous tile must have been read out
         if (i > 0 && !(ok = wait_or_abort(bar(ACC_FREE), (i - 1) & 1, abort_flag))) break;
         tc_fence_after();
-        for (int kb = 0; kb < nkb; ++kb, ++g) {
-          const int s = g % NST, use = g / NST;
+        for (int kb = 0; kb < nkb; kb += ksub) {
           if (!(ok = wait_or_abort(bar(FULL0 + s), use & 1, abort_flag))) break;
           tc_fence_after();
-          const uint32_t a = ring + s * stage_bytes, bsm = a + a_bytes;
+          const uint64_t da = desc0 + static_cast<uint64_t>((s * stage_bytes) >> 4);
+          const uint64_t db = da + static_cast<uint64_t>(a_bytes >> 4);
+          for (int j = 0; j < ksub; ++j) {
+            const uint64_t off = static_cast<uint64_t>((j * sub_bytes) >> 4);
 #pragma unroll
-          for (int ks = 0; ks < BK / 16; ++ks)
-            umma_ss(tmem, umma_desc(a + ks * 32, 16, 1024), umma_desc(bsm + ks * 32, 16, 1024), idesc, (kb > 0 || ks > 0) ? 1u : 0u);
+            for (int ks = 0; ks < BK / 16; ++ks)
+              umma_ss(tmem, da + off + 2 * ks, db + off + 2 * ks, idesc, (kb > 0 || j > 0 || ks > 0) ? 1u : 0u);
+          }
           umma_commit(bar(EMPTY0 + s));  // the stage is free once these products have read it
+          if (++s == NST) {
+            s = 0;
+            ++use;
+          }
         }
         if (ok) umma_commit(bar(ACC_FULL));
       }
@@ -312,7 +330,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_allreduce_kernel(const __gri
 // mode: 0 = that rule, 1 = one shot where it fits, 2 = two shots.  bn == 0: the shape or the cell
 // areas do not allow the kernel.
 struct Plan {
-  int bn = 0, a_rows = 0, nst = 0, one_shot = 0;
+  int bn = 0, a_rows = 0, ksub = 0, nst = 0, one_shot = 0;
 };
 static Plan make_plan(int64_t m, int64_t n, int64_t k, int world, int64_t stage_bytes, int nblocks, int mode) {
   Plan pl;
@@ -335,7 +353,9 @@ static Plan make_plan(int64_t m, int64_t n, int64_t k, int world, int64_t stage_
   else if (!two_fits) return pl;
   pl.bn = bn;
   pl.a_rows = ntm > 1 ? BM : static_cast<int>((m + 15) / 16 * 16);
-  const int stage = (pl.a_rows + bn) * 128;
+  const int sub = (pl.a_rows + bn) * 128;
+  pl.ksub = sub <= 12 * 1024 ? 4 : sub <= 24 * 1024 ? 2 : 1;
+  const int stage = sub * pl.ksub;
   pl.nst = RING_BYTES / stage < MAX_NST ? RING_BYTES / stage : MAX_NST;
   return pl;
 }
@@ -398,6 +418,7 @@ extern "C" int nvllm_ar_gemm_allreduce(const void* x, int64_t x_stride, const vo
   p.k = static_cast<int>(k);
   p.bn = bn;
   p.a_rows = pl.a_rows;
+  p.ksub = pl.ksub;
   p.nst = pl.nst;
   p.one_shot = pl.one_shot;
   p.rank = s->rank;
@@ -447,6 +468,7 @@ extern "C" int nvllm_ar_gemm_allreduce_emulated(int32_t world, const void* const
   p.k = static_cast<int>(k);
   p.bn = bn;
   p.a_rows = pl.a_rows;
+  p.ksub = pl.ksub;
   p.nst = pl.nst;
   p.one_shot = pl.one_shot;
   p.rank = -1;
@@ -468,3 +490,4 @@ extern "C" int nvllm_ar_gemm_allreduce_emulated(int32_t world, const void* const
   }
   return NVLLM_OK;
 }
+

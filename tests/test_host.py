@@ -123,3 +123,32 @@ def test_all_reduce_protocol_choice_is_host_arithmetic(lib):
     assert protocol_for(2 << 20, 8, mb, forced=2) == "one-shot"
     assert protocol_for(2 << 20, 2, mb, forced=3) == "cells"           # two shots need more than two ranks
     assert protocol_for(2 << 20, 8, mb, forced=1) == "cells-two-shot"  # cells to every peer do not fit: 2 x 2 MiB x 8 > 8 MiB
+
+
+def test_fused_projection_tile_choice_is_host_arithmetic(lib):
+    """Tile width of the projection fused with its all-reduce: the narrowest of 32 / 64 / 128 columns
+    that leaves one tile per thread block (128 blocks), 0 for shapes the kernel refuses."""
+    mb = 8 << 20
+    assert lib.nvllm_ar_gemm_tile(16, 4096, 512, 8, mb) == 32
+    assert lib.nvllm_ar_gemm_tile(256, 4096, 1536, 8, mb) == 64
+    assert lib.nvllm_ar_gemm_tile(512, 4096, 512, 8, mb) == 128
+    assert lib.nvllm_ar_gemm_tile(256, 1024, 1024, 2, mb) == 32
+    assert lib.nvllm_ar_gemm_tile(1024, 4096, 512, 8, mb) == 0   # cell areas too small
+    assert lib.nvllm_ar_gemm_tile(256, 4096, 512, 8, 1 << 20) == 0
+    assert lib.nvllm_ar_gemm_tile(8, 4096, 100, 2, mb) == 0      # k not a multiple of 8
+    assert lib.nvllm_ar_gemm_tile(8, 48, 64, 2, mb) == 0         # n not a multiple of 32
+    assert lib.nvllm_ar_gemm_tile(8, 4096, 512, 9, mb) == 0      # more ranks than the areas have regions for
+
+
+def test_oracle_row_parallel_projection_rounds_every_rank_once():
+    """The oracle's partials are bf16 (what each rank's GEMM returns), not fp32: the sum of rounded
+    partials differs from the rounded product over the whole k."""
+    g = torch.Generator().manual_seed(3)
+    xs = [torch.randn(4, 64, generator=g).to(torch.bfloat16) for _ in range(4)]
+    ws = [torch.randn(32, 64, generator=g).to(torch.bfloat16) for _ in range(4)]
+    got = R.row_parallel_linear_ref(xs, ws)
+    partials = [(x.float() @ w.float().t()).to(torch.bfloat16) for x, w in zip(xs, ws)]
+    assert torch.equal(got, R.allreduce_ref(partials))
+    whole = (torch.cat(xs, 1).float() @ torch.cat(ws, 1).float().t()).to(torch.bfloat16)
+    assert got.shape == whole.shape and not torch.equal(got, whole)
+    assert float((got.float() - whole.float()).abs().max()) <= 4 * 2.0 ** -8 * float(whole.float().abs().max())
