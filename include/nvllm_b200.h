@@ -351,8 +351,8 @@ NVLLM_API int nvllm_ar_allreduce_emulated(int32_t world, const void* const* inpu
  * makes the same calls in the same order, and calls may be mixed freely with nvllm_ar_allreduce.
  * x, weight, out: 16-byte aligned, row strides (elements) multiples of 8; k a multiple of 8, n of 32.
  * nvllm_ar_gemm_tile() returns the tile width (32, 64 or 128) the call would use, or 0 when the
- * shape does not fit the cell areas (4 * n * 128 * ceil(m / 128) bytes needed out of max_bytes) or
- * has fewer tiles than ranks; such shapes are refused with NVLLM_E_GEOMETRY (use the unfused pair).
+ * shape does not fit the cell areas (4 * n * 128 * ceil(m / 128) bytes needed out of max_bytes; 2, 4
+ * or 8 ranks); such shapes are refused with NVLLM_E_GEOMETRY (use the unfused pair).
  * Pure host arithmetic; no device needed. */
 NVLLM_API int nvllm_ar_gemm_tile(int64_t m, int64_t n, int64_t k, int32_t world, int64_t max_bytes);
 NVLLM_API int nvllm_ar_gemm_allreduce(const void* x, int64_t x_stride, const void* weight, int64_t w_stride, void* out,

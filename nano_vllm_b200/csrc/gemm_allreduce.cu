@@ -4,19 +4,24 @@
 // tensor-parallel rank and sums the partial outputs with dist.all_reduce: two launches and a pass
 // of the [tokens, hidden] partial through HBM.  Here the product runs on the tcgen05 tensor cores
 // (operands by TMA tile loads into a ring of shared-memory stages, accumulator in TMEM) and the
-// epilogue that reads the accumulator IS the all-reduce, in the flagged-cell two-shot protocol of
-// allreduce.cu, tile by tile:
+// epilogue that reads the accumulator IS the all-reduce, in the flagged-cell protocols of
+// allreduce.cu, tile by tile.  Two shots:
 //
 //   * the output is cut into tiles of 128 rows x bn columns (bn = 32, 64 or 128, the smallest
-//     that leaves at most one tile per thread block); tile t is owned by rank t mod world;
+//     that leaves at most one tile per thread block), a tile into groups of 4 columns (one cell per
+//     row); group c of tile t is owned by rank (t + c) mod world, so every block of every rank
+//     pushes, sums and collects the same amount;
 //   * every rank rounds its fp32 partial of a tile to bf16 (what F.linear would have returned);
-//     a rank that does not own the tile pushes it as cells {d0, call count, d1, call count}
-//     straight from registers into the owner's cell area, region [tile slot][source rank];
-//   * the owner adds the partials in rank order in fp32 as the cells arrive, rounds once, writes
-//     its own output and pushes the result cells into every peer's result-cell area;
-//   * the other ranks copy the tile from their result-cell area to their output.
-// A cell of a tile lives at (column group * 128 + row) * 16 bytes, so the 32 lanes of a warp
-// (32 consecutive accumulator rows) write 512 contiguous bytes per store instruction.
+//     the cells {d0, call count, d1, call count} of the groups it does not own go straight from
+//     registers into the owner's cell area, region [tile][source rank][owner's k-th group];
+//   * the owner adds the partials of its groups in rank order in fp32 as the cells arrive (all
+//     sources' cells in flight at once), rounds once, writes its own output and pushes the result
+//     cells into every peer's result-cell area;
+//   * the other ranks copy those groups from their result-cell area to their output.
+// At two ranks, and for small outputs at more (the rule of the plain all-reduce), one shot instead:
+// every rank pushes its partial of every tile to every peer and sums for itself, one NVLink
+// crossing.  A cell of a tile lives at (column group * 128 + row) * 16 bytes, so the 32 lanes of
+// a warp (32 consecutive accumulator rows) write 512 contiguous bytes per store instruction.
 //
 // The kernel uses the same grid, the same per-block call counts and the same two alternating cell
 // areas as the cell protocols of the plain all-reduce, so calls of either kind may follow each
@@ -210,12 +215,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_allreduce_kernel(const __gri
       for (int q = 0; q < 4; ++q) dst[q] = make_uint4(res[4 * q], res[4 * q + 1], res[4 * q + 2], res[4 * q + 3]);
     };
 
+    auto store_cell = [&](int t, int c, uint32_t lo, uint32_t hi) {  // 4 columns of this thread's output row
+      const int mt = t / ntn, nt = t - mt * ntn;
+      *reinterpret_cast<uint2*>(p.out[mi] + static_cast<int64_t>(mt * BM + r) * p.out_stride + nt * bn + c * 4) = make_uint2(lo, hi);
+    };
+    const int64_t ctw = ct / w;  // two shots: cells of a tile that one rank owns
+
     int i = 0;
     bool ok = true;
     for (int t = b; t < tiles && ok; t += p.nblocks, ++i) {
       const int mt = t / ntn;
       const bool valid = mt * BM + r < p.m;
-      const int owner = p.one_shot ? rank : t % w, slot = p.one_shot ? t : t / w;
       if (!(ok = wait_or_abort(bar(ACC_FULL), i & 1, abort_flag))) break;
       tc_fence_after();
       for (int ch = 0; ch < bn / 32; ++ch) {
@@ -233,79 +243,107 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_allreduce_kernel(const __gri
         for (int q = 0; q < 16; ++q) pk[q] = pack_bf16x2(__uint_as_float(v[2 * q]), __uint_as_float(v[2 * q + 1]));
         if (!valid) continue;
         const int64_t idx0 = static_cast<int64_t>(ch * 8) * 128 + r;  // cell (column group ch*8 + cc, row r) = idx0 + cc * 128
-        if (owner != rank) {
-          uint4* dst = reinterpret_cast<uint4*>(p.peers.base[owner] + area1) + (static_cast<int64_t>(slot) * w + rank) * ct + idx0;
-#pragma unroll
-          for (int cc = 0; cc < 8; ++cc) st_volatile16(dst + cc * 128, make_uint4(pk[2 * cc], e, pk[2 * cc + 1], e));
-          continue;
-        }
-        if (p.one_shot) {  // every rank sums: my partial goes to every peer
+        if (p.one_shot) {
+          // every rank sums every cell: my partial goes to every peer, region [tile][source]
           for (int k = 1; k < w; ++k) {
             const int j = (rank + k) % w;
-            uint4* dst = reinterpret_cast<uint4*>(p.peers.base[j] + area1) + (static_cast<int64_t>(slot) * w + rank) * ct + idx0;
+            uint4* dst = reinterpret_cast<uint4*>(p.peers.base[j] + area1) + (static_cast<int64_t>(t) * w + rank) * ct + idx0;
 #pragma unroll
             for (int cc = 0; cc < 8; ++cc) st_volatile16(dst + cc * 128, make_uint4(pk[2 * cc], e, pk[2 * cc + 1], e));
           }
-        }
-        // owner: partials in rank order; the next source's cells are in flight while one is added
-        float acc[8][4];
+          // partials in rank order; the next source's cells are in flight while one is added
+          float acc[8][4];
 #pragma unroll
-        for (int cc = 0; cc < 8; ++cc) acc[cc][0] = acc[cc][1] = acc[cc][2] = acc[cc][3] = 0.f;
-        const uint4* mine = reinterpret_cast<const uint4*>(own + area1) + static_cast<int64_t>(slot) * w * ct + idx0;
-        uint4 cur[8], nxt[8];
-        auto fetch = [&](int src, uint4 (&buf)[8]) {
-          if (src >= w || src == rank) return;
+          for (int cc = 0; cc < 8; ++cc) acc[cc][0] = acc[cc][1] = acc[cc][2] = acc[cc][3] = 0.f;
+          const uint4* mine = reinterpret_cast<const uint4*>(own + area1) + static_cast<int64_t>(t) * w * ct + idx0;
+          uint4 cur[8], nxt[8];
+          auto fetch = [&](int src, uint4 (&buf)[8]) {
+            if (src >= w || src == rank) return;
 #pragma unroll
-          for (int cc = 0; cc < 8; ++cc) buf[cc] = ld_volatile16(mine + src * ct + cc * 128);
-        };
-        fetch(0, cur);
-        for (int src = 0; src < w; ++src) {
-          fetch(src + 1, nxt);
-          if (src == rank) {
+            for (int cc = 0; cc < 8; ++cc) buf[cc] = ld_volatile16(mine + src * ct + cc * 128);
+          };
+          fetch(0, cur);
+          for (int src = 0; src < w; ++src) {
+            fetch(src + 1, nxt);
+            if (src == rank) {
 #pragma unroll
-            for (int cc = 0; cc < 8; ++cc) add4(acc[cc], pk[2 * cc], pk[2 * cc + 1]);
-          } else {
+              for (int cc = 0; cc < 8; ++cc) add4(acc[cc], pk[2 * cc], pk[2 * cc + 1]);
+            } else {
 #pragma unroll
-            for (int cc = 0; cc < 8; ++cc) {
-              const uint4 c = wait_cell(mine + src * ct + cc * 128, cur[cc]);
-              add4(acc[cc], c.x, c.z);
+              for (int cc = 0; cc < 8; ++cc) {
+                const uint4 c = wait_cell(mine + src * ct + cc * 128, cur[cc]);
+                add4(acc[cc], c.x, c.z);
+              }
             }
-          }
 #pragma unroll
-          for (int cc = 0; cc < 8; ++cc) cur[cc] = nxt[cc];
+            for (int cc = 0; cc < 8; ++cc) cur[cc] = nxt[cc];
+          }
+          uint32_t res[16];
+#pragma unroll
+          for (int cc = 0; cc < 8; ++cc) {
+            res[2 * cc] = pack_bf16x2(acc[cc][0], acc[cc][1]);
+            res[2 * cc + 1] = pack_bf16x2(acc[cc][2], acc[cc][3]);
+          }
+          store_row(t, ch, res);
+          continue;
         }
-        uint32_t res[16];
+        // Two shots.  Column group c of tile t (4 columns of all 128 rows) is owned by rank
+        // (t + c) mod w, so every block of every rank pushes, sums and collects the same amount.
+        // First my partials of the groups other ranks own: region [tile][source][owner's k-th group].
 #pragma unroll
         for (int cc = 0; cc < 8; ++cc) {
-          res[2 * cc] = pack_bf16x2(acc[cc][0], acc[cc][1]);
-          res[2 * cc + 1] = pack_bf16x2(acc[cc][2], acc[cc][3]);
+          const int c = ch * 8 + cc, o = (t + c) % w;
+          if (o != rank)
+            st_volatile16(reinterpret_cast<uint4*>(p.peers.base[o] + area1) + (static_cast<int64_t>(t) * w + rank) * ctw + (c / w) * 128 + r,
+                          make_uint4(pk[2 * cc], e, pk[2 * cc + 1], e));
         }
-        for (int k = 1; k < w && !p.one_shot; ++k) {
-          const int j = (rank + k) % w;  // every owner starts with another peer
-          uint4* dst = reinterpret_cast<uint4*>(p.peers.base[j] + area2) + static_cast<int64_t>(t) * ct + idx0;
+        // Then the groups I own: all sources' cells in flight at once, added in rank order.
 #pragma unroll
-          for (int cc = 0; cc < 8; ++cc) st_volatile16(dst + cc * 128, make_uint4(res[2 * cc], e, res[2 * cc + 1], e));
+        for (int cc = 0; cc < 8; ++cc) {
+          const int c = ch * 8 + cc;
+          if ((t + c) % w != rank) continue;
+          const uint4* mine = reinterpret_cast<const uint4*>(own + area1) + static_cast<int64_t>(t) * w * ctw + (c / w) * 128 + r;
+          uint4 got[kMaxRanks];
+#pragma unroll
+          for (int src = 0; src < kMaxRanks; ++src)
+            if (src < w && src != rank) got[src] = ld_volatile16(mine + src * ctw);
+          float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int src = 0; src < kMaxRanks; ++src) {
+            if (src >= w) continue;
+            if (src == rank) {
+              add4(acc, pk[2 * cc], pk[2 * cc + 1]);
+            } else {
+              const uint4 cell = wait_cell(mine + src * ctw, got[src]);
+              add4(acc, cell.x, cell.z);
+            }
+          }
+          const uint32_t lo = pack_bf16x2(acc[0], acc[1]), hi = pack_bf16x2(acc[2], acc[3]);
+          for (int k = 1; k < w; ++k) {
+            const int j = (rank + k) % w;  // every owner starts with another peer
+            st_volatile16(reinterpret_cast<uint4*>(p.peers.base[j] + area2) + static_cast<int64_t>(t) * ct + idx0 + cc * 128,
+                          make_uint4(lo, e, hi, e));
+          }
+          store_cell(t, c, lo, hi);
         }
-        store_row(t, ch, res);
       }
     }
-    // the tiles that other ranks own arrive in this rank's result-cell area
+    // two shots: the column groups that other ranks own arrive in this rank's result-cell area
     for (int t = b; t < tiles && ok && !p.one_shot; t += p.nblocks) {
       const int mt = t / ntn;
-      if (t % w == rank || mt * BM + r >= p.m) continue;
+      if (mt * BM + r >= p.m) continue;
       const uint4* results = reinterpret_cast<const uint4*>(own + area2) + static_cast<int64_t>(t) * ct + r;
       for (int ch = 0; ch < bn / 32; ++ch) {
         uint4 c[8];
 #pragma unroll
-        for (int cc = 0; cc < 8; ++cc) c[cc] = ld_volatile16(results + (ch * 8 + cc) * 128);
-        uint32_t res[16];
+        for (int cc = 0; cc < 8; ++cc)
+          if ((t + ch * 8 + cc) % w != rank) c[cc] = ld_volatile16(results + (ch * 8 + cc) * 128);
 #pragma unroll
         for (int cc = 0; cc < 8; ++cc) {
+          if ((t + ch * 8 + cc) % w == rank) continue;
           c[cc] = wait_cell(results + (ch * 8 + cc) * 128, c[cc]);
-          res[2 * cc] = c[cc].x;
-          res[2 * cc + 1] = c[cc].z;
+          store_cell(t, ch * 8 + cc, c[cc].x, c[cc].z);
         }
-        store_row(t, ch, res);
       }
     }
   }
@@ -345,9 +383,8 @@ static Plan make_plan(int64_t m, int64_t n, int64_t k, int world, int64_t stage_
   if (!bn) return pl;
   const int64_t tiles = ntm * (n / bn), cell_bytes = 32 * static_cast<int64_t>(bn) * 16;
   const bool one_fits = tiles * world * cell_bytes <= stage_bytes;
-  // two shots: every rank must own a tile (the two-area argument needs a cell from every peer in every call)
-  const bool two_fits = tiles >= world && (tiles + world - 1) / world * world * cell_bytes <= stage_bytes &&
-                        tiles * cell_bytes <= stage_bytes;
+  // two shots: a tile's 4-column groups are dealt out to the ranks in turn (8 groups at bn = 32)
+  const bool two_fits = (world == 2 || world == 4 || world == 8) && tiles * cell_bytes <= stage_bytes;
   const bool one_preferred = world == 2 || m * n * 2 * (world - 1) * (2 * world - 4) / world <= kCellsOneShotExtraBytes;
   if (one_fits && (mode == 1 || (mode == 0 && one_preferred) || !two_fits)) pl.one_shot = 1;
   else if (!two_fits) return pl;
