@@ -136,3 +136,60 @@ assert head(x).shape == (5, 6)
 print("ok")
 """)
     assert out == "ok"
+
+
+def test_row_parallel_forward_picks_the_fused_projection_only_where_it_applies():
+    """RowParallelLinear.forward after fuse_all_reduce(fuse_gemm=True): a bias-free projection of at
+    most 512 tokens whose shape the kernel takes goes through ONE call (product + sum); a bias, a
+    larger batch or a refused shape use F.linear followed by the peer sum (small tensors) or
+    dist.all_reduce (large ones); without fuse_gemm the fused call is never made."""
+    out = _run(PRELUDE + """
+from nano_vllm_b200 import plugin, allreduce as AR
+plugin.install()
+import torch, torch.distributed as dist
+import nanovllm.layers.linear as linear
+calls = []
+class FakeAR:
+    def __init__(self, rank, world, max_bytes, wait_ms=None):
+        calls.append(("init", rank, world))
+    def linear_fits(self, x, w):
+        return x.shape[1] % 8 == 0
+    def linear_all_reduce(self, x, w):
+        calls.append(("fused", tuple(x.shape)))
+        return x @ w.t()
+    def preferred(self, y):
+        return y.numel() <= 4096
+    def all_reduce(self, y):
+        calls.append(("peer", tuple(y.shape)))
+        return y
+AR.PeerAllReduce = FakeAR
+dist.get_rank, dist.get_world_size = (lambda: 1), (lambda: 2)
+dist.all_reduce = lambda y: calls.append(("nccl", tuple(y.shape)))
+torch.cuda.is_current_stream_capturing = lambda: False
+def layer(k, n, bias):
+    m = object.__new__(linear.RowParallelLinear)
+    torch.nn.Module.__init__(m)
+    m.tp_size, m.tp_rank = 2, 1
+    m.weight = torch.nn.Parameter(torch.randn(n, k))
+    m.bias = torch.nn.Parameter(torch.randn(n)) if bias else None
+    return m
+plugin.fuse_all_reduce(fuse_gemm=True)
+x = torch.randn(16, 64)
+y = layer(64, 32, False)(x)
+assert calls == [("init", 1, 2), ("fused", (16, 64))] and y.shape == (16, 32)
+del calls[:]
+layer(64, 32, True)(x)                       # bias: unfused, small -> peer sum
+layer(64, 32, False)(torch.randn(600, 64))   # more than 512 tokens: unfused, large -> NCCL
+layer(60, 32, False)(torch.randn(16, 60))    # shape the kernel refuses
+assert calls == [("peer", (16, 32)), ("nccl", (600, 32)), ("peer", (16, 32))], calls
+del calls[:]
+plugin.fuse_all_reduce()
+layer(64, 32, False)(x)
+assert calls == [("init", 1, 2), ("peer", (16, 32))], calls
+one = layer(64, 32, True)
+one.tp_size, one.tp_rank = 1, 0
+del calls[:]
+assert torch.allclose(one(x), x @ one.weight.t() + one.bias) and calls == []
+print("ok")
+""")
+    assert out == "ok"
