@@ -7,8 +7,11 @@
 // their row of S with tcgen05.ld, write P as packed bf16 over it with tcgen05.st; O += P V (TS
 // form: P from TMEM, V as an MN-major shared-memory operand); Q, K, V arrive by TMA tile loads
 // (128-byte swizzle, no multicast) into a two-stage ring; one tcgen05.commit per MMA group.
-// Six warps: 0-3 softmax / correction / epilogue, warp 4 lane 0 = TMA producer, warp 5 lane 0 =
-// MMA issuer.  A thread block does not end with its query tile: two blocks per SM stay resident
+// Twelve warps: 0-3 softmax / correction (thread = query row), 4-7 epilogue (same rows: when an
+// item's last P V product is done they normalise O and store it while the softmax warps are
+// already in the next item's first tile), warp 8 lane 0 = TMA producer, warp 9 lane 0 = MMA issuer;
+// the three warp groups trade registers at start-up (setmaxnreg) so that two such blocks fit an
+// SM.  A thread block does not end with its query tile: two blocks per SM stay resident
 // for the whole launch, keep their TMEM allocation and barriers, and pull work items (sequence,
 // query tile, head group) from a global counter.  Under grouped-query attention the 128 rows of a tile are
 // 128/n tokens x n query heads that share a KV head (n = 1, 2, 4 or 8), not 128 tokens of one
@@ -28,10 +31,11 @@
 // memory (ITEM_FULL / ITEM_FREE barriers).  All rings keep running across items: tile t of the
 // block's life uses stage t&1 and barrier phase (t>>1)&1, so the next item's first K/V tiles
 // are fetched under the current item's last products.  The first P V product of an item waits
-// for the previous item's O to be read (O_FREE).  The epilogue needs no block-wide buffer: a
-// softmax warp owns the same 32 rows in TMEM and in the output, and passes them 32 columns at
-// a time through a private 2 KB patch of shared memory to turn row-per-lane registers into
-// 64-byte row segments.
+// for the previous item's O to be read (O_FREE); the softmax warps leave each row's 1 / sum in
+// shared memory (EPI_FULL) and move on.  The epilogue needs no block-wide buffer: an epilogue
+// warp owns the same 32 rows in TMEM and in the output, and passes them 32 columns at a time
+// through a private 2 KB patch of shared memory to turn row-per-lane registers into 64-byte row
+// segments.
 #include <atomic>
 #include <cstdlib>
 
@@ -48,8 +52,15 @@ using namespace tc;
 constexpr int MAX_BATCH = kPrefillMaxBatch;  // prefix array of query tiles per sequence lives in shared memory
 constexpr int SORT_BATCH = 256;  // batches up to this size are ranked by length (B^2 / 192 compares per thread)
 enum PBar {
-  ITEM_FULL0 = tc::NUM_BARS, ITEM_FULL1, ITEM_FREE0, ITEM_FREE1, O_FREE, P_NUM_BARS
+  ITEM_FULL0 = tc::NUM_BARS, ITEM_FULL1, ITEM_FREE0, ITEM_FREE1, O_FREE, EPI_FULL0, EPI_FULL1, P_NUM_BARS
 };
+// Twelve warps in three groups of four: softmax, epilogue, and (TMA producer, MMA issuer, two idle).
+// Registers are handed over between the groups at start-up (setmaxnreg): two blocks of 384 threads
+// per SM leave 80 per thread at launch; the softmax rows need about twice that, the other groups
+// a fraction.  128 x (RS + RE + RX) = 384 x 80.
+constexpr int NTHREADS_P = 384;
+constexpr int REGS_SOFTMAX = 136, REGS_EPILOGUE = 64, REGS_OTHER = 40;
+static_assert(128 * (REGS_SOFTMAX + REGS_EPILOGUE + REGS_OTHER) <= 384 * 80, "register pool of a block");
 // Shared-memory layout and tile sizes for one head_dim (64 or 128).  A tile row is split into
 // 64-element (128-byte) sub-tiles, the unit of the 128-byte swizzle.
 template <int D_>
@@ -65,7 +76,8 @@ struct Geo {
   static constexpr int OFF_MISC = OFF_SLOTS + 64;          // tmem address, abort flag
   static constexpr int OFF_PREFIX = OFF_MISC + 64;         // (MAX_BATCH + 1) ints
   static constexpr int OFF_ORDER = OFF_PREFIX + (MAX_BATCH + 1) * 4 + 60;  // MAX_BATCH u16: sequences, longest first
-  static constexpr int SMEM = OFF_ORDER + MAX_BATCH * 2 + 1024;
+  static constexpr int OFF_INV = OFF_ORDER + MAX_BATCH * 2;  // 2 items x 128 rows: 1 / row sum, softmax -> epilogue
+  static constexpr int SMEM = OFF_INV + 2 * 128 * 4 + 1024;
   static constexpr int OCH = D / 32;      // 32-column chunks of O
   static constexpr int ROWB = D * 2;      // bytes of one output row
   static constexpr int PIECES = D / 8;    // 16-byte pieces of one row
@@ -83,7 +95,7 @@ struct Item {
 };
 
 template <int D>
-__global__ void __launch_bounds__(tc::NTHREADS, 2)
+__global__ void __launch_bounds__(tcp::NTHREADS_P, 2)
 prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tmap_q,
                    const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                    const int counter_slot) {
@@ -113,12 +125,12 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
 
   // Rank the sequences by key length, longest first (ties by index): rank = how many come before.
   if (p.batch <= SORT_BATCH) {
-    for (int b = tid; b < p.batch; b += NTHREADS) prefix[b] = p.cu_k[b + 1] - p.cu_k[b];  // lengths, for a moment
+    for (int b = tid; b < p.batch; b += NTHREADS_P) prefix[b] = p.cu_k[b + 1] - p.cu_k[b];  // lengths, for a moment
     __syncthreads();
-    int my_rank[(SORT_BATCH + NTHREADS - 1) / NTHREADS];
+    int my_rank[(SORT_BATCH + NTHREADS_P - 1) / NTHREADS_P];
 #pragma unroll
-    for (int k = 0; k < (SORT_BATCH + NTHREADS - 1) / NTHREADS; ++k) {
-      const int b = tid + k * NTHREADS;
+    for (int k = 0; k < (SORT_BATCH + NTHREADS_P - 1) / NTHREADS_P; ++k) {
+      const int b = tid + k * NTHREADS_P;
       int rank = 0;
       if (b < p.batch) {
         const int mine = prefix[b];
@@ -131,15 +143,15 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
     }
     __syncthreads();
 #pragma unroll
-    for (int k = 0; k < (SORT_BATCH + NTHREADS - 1) / NTHREADS; ++k) {
-      const int b = tid + k * NTHREADS;
+    for (int k = 0; k < (SORT_BATCH + NTHREADS_P - 1) / NTHREADS_P; ++k) {
+      const int b = tid + k * NTHREADS_P;
       if (b < p.batch) order[my_rank[k]] = static_cast<unsigned short>(b);
     }
   } else {
-    for (int b = tid; b < p.batch; b += NTHREADS) order[b] = static_cast<unsigned short>(b);
+    for (int b = tid; b < p.batch; b += NTHREADS_P) order[b] = static_cast<unsigned short>(b);
   }
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     // query tiles per sequence, in that order -> exclusive prefix sum (warp scan, 32 at a time)
     int carry = 0;
     for (int i0 = 0; i0 < p.batch; i0 += 32) {
@@ -161,9 +173,11 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
     if (lane == 0) {
       prefix[p.batch] = carry;
       for (int i = 0; i < P_NUM_BARS; ++i) {
-        const uint32_t count = (i == P_FULL0 || i == P_FULL1 || i == O_FREE) ? 4u
-                               : (i == ITEM_FREE0 || i == ITEM_FREE1)                            ? 5u
-                                                                                                 : 1u;
+        // four softmax warps fill P and the normalisers; four epilogue warps free O; an item slot is
+        // free when the softmax warps, the epilogue warps and the MMA issuer are done with it
+        const uint32_t count = (i == P_FULL0 || i == P_FULL1 || i == O_FREE || i == EPI_FULL0 || i == EPI_FULL1) ? 4u
+                               : (i == ITEM_FREE0 || i == ITEM_FREE1)                                               ? 9u
+                                                                                                                    : 1u;
         mbar_init(bar(i), count);
       }
       *abort_flag = 0;
@@ -173,7 +187,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
       prefetch_tmap(&tmap_v);
     }
   }
-  if (warp == 5) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+  if (warp == 9) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -188,7 +202,12 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
     return x;
   };
 
-  if (warp == 4) {
+  float* inv_buf = reinterpret_cast<float*>(base_ptr + G::OFF_INV);
+  // The register hand-over sits inside each group's own branch: the allocator bounds the code that
+  // follows a setmaxnreg on its path, and paths that merged again would all get the smallest bound.
+  if (warp >= 8) {
+   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_OTHER));
+   if (warp == 8) {
     // ------------------------------------------------------------------ producer lane
     if (lane == 0) {
       const int hgroups = p.hq / pack;
@@ -280,7 +299,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
         T += x.n_kv;
       }
     }
-  } else if (warp == 5) {
+   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc(BM, BN, 0, 0);
@@ -337,12 +356,13 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
         (void)mbar_wait(bar(DRAIN), 0);
       }
     }
-  } else {
+   }
+  } else if (warp < 4) {
     // ------------------------------------------------------------------ softmax rows
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_SOFTMAX));
     const int r = warp * 32 + lane;
     const int r_tok = r / pack;  // this row's token within the tile (== BMT for the unused rows of a 7-head tile)
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
-    unsigned char* stage = base_ptr + G::OFF_STAGE + warp * 2048;  // this warp's 32 rows x 64 B
     int T = 0;
     bool ok = true;
     for (int it = 0; ok; ++it) {
@@ -441,40 +461,62 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
       if (!ok) break;
       T += x.n_kv;
 
+      // the row's normaliser goes to the epilogue warps; this warp is done with the item
+      inv_buf[(it & 1) * 128 + r] = l > 0.f ? 1.f / l : 0.f;
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(bar(EPI_FULL0 + (it & 1)));
+        mbar_arrive(bar(ITEM_FREE0 + (it & 1)));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue rows
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_EPILOGUE));
+    // Same rows as softmax warp (warp - 4): a warp reaches the TMEM lanes 32 x (warp mod 4).
+    const int ew = warp - 4, r = ew * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(ew * 32) << 16;
+    unsigned char* stage = base_ptr + G::OFF_STAGE + ew * 2048;  // this warp's 32 rows x 64 B
+    int T = 0;
+    bool ok = true;
+    for (int it = 0; ok; ++it) {
+      if (!(ok = wait_or_abort(bar(ITEM_FULL0 + (it & 1)), (it >> 1) & 1, abort_flag))) break;
+      const Item x = read_item(it);
+      if (x.n_kv < 0) break;
+      T += x.n_kv;
+      if (!(ok = wait_or_abort(bar(EPI_FULL0 + (it & 1)), (it >> 1) & 1, abort_flag))) break;
+      const float inv = inv_buf[(it & 1) * 128 + r];
       // epilogue: O / l -> bf16; 32 columns at a time through this warp's patch of shared memory
       if (!(ok = wait_or_abort(bar(PV_DONE0 + ((T - 1) & 1)), ((T - 1) >> 1) & 1, abort_flag))) break;
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
       // lane -> (row, 16-byte piece) of the eight 64-byte row segments one store instruction writes
       const int srow = lane >> 2, spiece = lane & 3;
       __nv_bfloat16* out_tile = p.out + static_cast<int64_t>(x.q0 + x.m0) * p.out_stride + x.h * D;
       const int toks_valid = min(BMT, x.Lq - x.m0);
-      uint32_t ob[2][32];  // the load of the next 32 columns runs under the stores of the current ones
-      tmem_ld32(tmem_o + lane_addr, ob[0]);
 #pragma unroll
       for (int c = 0; c < OCH; ++c) {
-        uint32_t(&o)[32] = ob[c & 1];
+        uint32_t o[32];
+        tmem_ld32(tmem_o + lane_addr + c * 32, o);
         tmem_wait_ld();
-        if (c + 1 < OCH) tmem_ld32(tmem_o + lane_addr + (c + 1) * 32, ob[(c + 1) & 1]);
         if (c == OCH - 1) {  // O is in registers: the next item's first product may overwrite it
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(O_FREE));
         }
+        uint4 v[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          uint4 v;
-          v.x = pack_bf16x2(__uint_as_float(o[8 * k]) * inv, __uint_as_float(o[8 * k + 1]) * inv);
-          v.y = pack_bf16x2(__uint_as_float(o[8 * k + 2]) * inv, __uint_as_float(o[8 * k + 3]) * inv);
-          v.z = pack_bf16x2(__uint_as_float(o[8 * k + 4]) * inv, __uint_as_float(o[8 * k + 5]) * inv);
-          v.w = pack_bf16x2(__uint_as_float(o[8 * k + 6]) * inv, __uint_as_float(o[8 * k + 7]) * inv);
-          *reinterpret_cast<uint4*>(stage + lane * 64 + ((k ^ ((lane >> 1) & 3)) << 4)) = v;
+          v[k].x = pack_bf16x2(__uint_as_float(o[8 * k]) * inv, __uint_as_float(o[8 * k + 1]) * inv);
+          v[k].y = pack_bf16x2(__uint_as_float(o[8 * k + 2]) * inv, __uint_as_float(o[8 * k + 3]) * inv);
+          v[k].z = pack_bf16x2(__uint_as_float(o[8 * k + 4]) * inv, __uint_as_float(o[8 * k + 5]) * inv);
+          v[k].w = pack_bf16x2(__uint_as_float(o[8 * k + 6]) * inv, __uint_as_float(o[8 * k + 7]) * inv);
         }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) *reinterpret_cast<uint4*>(stage + lane * 64 + ((k ^ ((lane >> 1) & 3)) << 4)) = v[k];
         __syncwarp();
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int lr = i * 8 + srow;       // row within the warp's 32
-          const int row = warp * 32 + lr;    // row of the tile
+          const int row = ew * 32 + lr;      // row of the tile
           const int tok = row / pack, hh = row - tok * pack;
           const uint4 v = *reinterpret_cast<const uint4*>(stage + lr * 64 + ((spiece ^ ((lr >> 1) & 3)) << 4));
           if (tok < toks_valid)
@@ -497,7 +539,7 @@ prefill_tcp_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap tm
       __threadfence();
     }
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
   }
@@ -517,6 +559,15 @@ static int launch_prefill_tcp_t(const PrefillParams& p_in, int64_t total_q, int6
   if (!attr_done[dev]) {
     cudaError_t e = cudaFuncSetAttribute(prefill_tcp_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM);
     if (e != cudaSuccess) return fail(NVLLM_E_CUDA, "prefill (persistent): set-up failed: %s", cudaGetErrorString(e));
+    // The warp groups trade registers inside the pool the block gets at launch (threads x the kernel's
+    // register count); a build whose count is below the assumed 80 could never satisfy the softmax
+    // group's request, and that request waits without a bound.
+    cudaFuncAttributes attr;
+    e = cudaFuncGetAttributes(&attr, prefill_tcp_kernel<D>);
+    if (e != cudaSuccess) return fail(NVLLM_E_CUDA, "prefill (persistent): set-up failed: %s", cudaGetErrorString(e));
+    if (attr.numRegs * tcp::NTHREADS_P < 128 * (tcp::REGS_SOFTMAX + tcp::REGS_EPILOGUE + tcp::REGS_OTHER))
+      return fail(NVLLM_E_CUDA, "prefill (persistent): built with %d registers per thread, the warp groups' hand-over needs %d",
+                  attr.numRegs, 128 * (tcp::REGS_SOFTMAX + tcp::REGS_EPILOGUE + tcp::REGS_OTHER) / tcp::NTHREADS_P);
     attr_done[dev] = true;
   }
   // heads packed into a query tile: the largest divisor of the group size that is at most 8
@@ -546,7 +597,7 @@ static int launch_prefill_tcp_t(const PrefillParams& p_in, int64_t total_q, int6
   if (max_items < grid) grid = static_cast<int>(max_items);
   // the two head_dim instantiations share the counter array: give each its own half
   const int slot = static_cast<int>(launch_seq.fetch_add(1) % (tcp::NUM_SLOTS / 2)) + (D == 64 ? tcp::NUM_SLOTS / 2 : 0);
-  prefill_tcp_kernel<D><<<grid, tc::NTHREADS, G::SMEM, stream>>>(p, mq, mk, mv, slot);
+  prefill_tcp_kernel<D><<<grid, tcp::NTHREADS_P, G::SMEM, stream>>>(p, mq, mk, mv, slot);
   count_launch();
   return check_launch("prefill (tcgen05, persistent) launch");
 }
