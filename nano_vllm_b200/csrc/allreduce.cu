@@ -190,31 +190,42 @@ __device__ void allreduce_cells_block(const Params& p, int rank, int b, int nblo
       st_volatile16(dst, cell);
     }
   }
-  // collect: own area, regions [source = r]; sum in rank order
+  // collect: own area, regions [source = r]; every source's cell is requested before the first is
+  // looked at (one memory latency instead of world-1 in a row), then summed in rank order
   bool gave_up = s_abort;
+  // a cell of this call (first try: the value already loaded), or after the clock limit whatever is there
+  auto settle = [&](const uint4* src, uint4 v) {
+    if (!gave_up && (v.y != e || v.w != e)) {
+      const long long t0 = clock64();
+      do {
+        v = ld_volatile16(src);
+        if (clock64() - t0 > p.wait_cycles) {
+          atomicOr(p.status, NVLLM_STATUS_TIMEOUT);
+          *reinterpret_cast<volatile uint32_t*>(broken) = 1;
+          gave_up = true;
+          break;
+        }
+      } while (v.y != e || v.w != e);
+    }
+    return v;
+  };
   for (int64_t c = c0 + tid; c < c1; c += blockDim.x) {
+    const uint4* mine = reinterpret_cast<const uint4*>(own + area_off) + c;
+    uint4 got[kMaxRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < p.world && r != rank) got[r] = ld_volatile16(mine + r * cells_cap);
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int r = 0; r < p.world; ++r) {
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r) {
+      if (r >= p.world) continue;
       if (r == rank) {
         const uint2 d = load_own(c);
         add4(acc, d.x, d.y);
-        continue;
+      } else {
+        const uint4 v = settle(mine + r * cells_cap, got[r]);
+        add4(acc, v.x, v.z);
       }
-      const uint4* src = reinterpret_cast<const uint4*>(own + area_off) + r * cells_cap + c;
-      uint4 v = ld_volatile16(src);
-      if (!gave_up && (v.y != e || v.w != e)) {
-        const long long t0 = clock64();
-        do {
-          v = ld_volatile16(src);
-          if (clock64() - t0 > p.wait_cycles) {
-            atomicOr(p.status, NVLLM_STATUS_TIMEOUT);
-            *reinterpret_cast<volatile uint32_t*>(broken) = 1;
-            gave_up = true;
-            break;
-          }
-        } while (v.y != e || v.w != e);
-      }
-      add4(acc, v.x, v.z);
     }
     uint2 o;
     o.x = pack_bf16x2(acc[0], acc[1]);
@@ -270,17 +281,20 @@ __device__ void allreduce_cells_twoshot_block(const Params& p, int rank, int b, 
         if (4 * c + k < n_elems) out_e[4 * c + k] = t[k];
     }
   };
-  // this block's part [lo, hi) of slice j (slices and parts in cells)
+  // this block's part [lo, hi) of slice j (slices and parts in cells); 32-bit arithmetic (at most
+  // 2^22 cells x 8 ranks, a slice x 128 blocks): a 64-bit division costs ~100 cycles, and there
+  // are four per slice and phase
+  const uint32_t nc32 = static_cast<uint32_t>(n_cells), w32 = static_cast<uint32_t>(w), nb32 = static_cast<uint32_t>(nblocks);
   auto part = [&](int j, int64_t& s0, int64_t& lo, int64_t& hi) {
-    s0 = n_cells * j / w;
-    const int64_t len = n_cells * (j + 1) / w - s0;
-    lo = s0 + len * b / nblocks;
-    hi = s0 + len * (b + 1) / nblocks;
+    const uint32_t a = nc32 * static_cast<uint32_t>(j) / w32;
+    const uint32_t len = nc32 * static_cast<uint32_t>(j + 1) / w32 - a;
+    s0 = a;
+    lo = a + len * static_cast<uint32_t>(b) / nb32;
+    hi = a + len * static_cast<uint32_t>(b + 1) / nb32;
   };
   bool gave_up = s_abort;
-  // a cell of this call, or (after the clock limit) whatever is there
-  auto wait_cell = [&](const uint4* src) {
-    uint4 v = ld_volatile16(src);
+  // a cell of this call (first try: the value already loaded), or after the clock limit whatever is there
+  auto settle = [&](const uint4* src, uint4 v) {
     if (!gave_up && (v.y != e || v.w != e)) {
       const long long t0 = clock64();
       do {
@@ -313,13 +327,20 @@ __device__ void allreduce_cells_twoshot_block(const Params& p, int rank, int b, 
     part(rank, s0, lo, hi);
     const uint4* mine = reinterpret_cast<const uint4*>(own + area1);
     for (int64_t c = lo + tid; c < hi; c += blockDim.x) {
+      // every source's cell is requested before the first is looked at
+      uint4 got[kMaxRanks];
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < w && r != rank) got[r] = ld_volatile16(mine + r * cells_cap + (c - s0));
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
-      for (int r = 0; r < w; ++r) {
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r) {
+        if (r >= w) continue;
         if (r == rank) {
           const uint2 d = load_own(c);
           add4(acc, d.x, d.y);
         } else {
-          const uint4 v = wait_cell(mine + r * cells_cap + (c - s0));
+          const uint4 v = settle(mine + r * cells_cap + (c - s0), got[r]);
           add4(acc, v.x, v.z);
         }
       }
@@ -340,9 +361,17 @@ __device__ void allreduce_cells_twoshot_block(const Params& p, int rank, int b, 
     const int j = (rank + k) % w;
     int64_t s0, lo, hi;
     part(j, s0, lo, hi);
-    for (int64_t c = lo + tid; c < hi; c += blockDim.x) {
-      const uint4 v = wait_cell(results + c);
-      store_out(c, make_uint2(v.x, v.z));
+    for (int64_t c = lo + tid; c < hi; c += 4 * blockDim.x) {  // four cells in flight per thread
+      uint4 v[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (c + k * blockDim.x < hi) v[k] = ld_volatile16(results + c + k * blockDim.x);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (c + k * blockDim.x >= hi) continue;
+        v[k] = settle(results + c + k * blockDim.x, v[k]);
+        store_out(c + k * blockDim.x, make_uint2(v[k].x, v[k].z));
+      }
     }
   }
   __syncthreads();
@@ -446,12 +475,13 @@ __host__ __device__ inline int pick_protocol(int64_t n16, int64_t tail_elems, in
   const bool cells_fit = 2 * ((n_elems + 3) / 4 * 8) * world <= stage_bytes;
   const bool twoshot_fits = world > 2 && tail_elems == 0 && (n16 + world - 1) / world <= stage_bytes / 16 / world;
   const int64_t n_cells = (n_elems + 3) / 4;
-  const bool cells_twoshot_fits = world > 2 && (n_cells + world - 1) / world <= stage_bytes / 16 / world && n_cells * 16 <= stage_bytes;
+  const bool cells_twoshot_fits = world > 2 && (n_cells + world - 1) / world <= stage_bytes / 16 / world && n_cells * 16 <= stage_bytes &&
+                                  n_cells <= (1 << 25);  // the slices are cut with 32-bit arithmetic
   if (force == kCells && cells_fit) return kCells;
   if (force == kCellsTwoShot && cells_twoshot_fits) return kCellsTwoShot;
   if (force == kTwoShot && twoshot_fits) return kTwoShot;
   if (force == kOneShot) return kOneShot;
-  if (cells_fit && (world == 2 || n_elems * 2 * (world - 1) * (2 * world - 4) / world <= kCellsOneShotExtraBytes)) return kCells;
+  if (cells_fit && (world == 2 || n_elems * 2 <= kCellsOneShotMaxBytes)) return kCells;
   if (cells_twoshot_fits) return kCellsTwoShot;
   if (twoshot_fits) return kTwoShot;
   return kOneShot;

@@ -27,10 +27,10 @@ static_assert(kGrid <= kMaxBlocks, "flag slots");
 constexpr int kAreas = 8;  // staging 0/1, cells 0/1, result 0/1, result cells 0/1: max_bytes each
 enum Protocol { kAuto = 0, kCells = 1, kOneShot = 2, kTwoShot = 3, kCellsTwoShot = 4 };
 // At more than two ranks, cells to every peer put 2 x bytes x (w-1) on a rank's wire, cells in two
-// shots 4 x bytes x (w-1)/w but cost one more NVLink crossing (about 6 us measured at 4 ranks).
-// The first wins while its extra bytes, bytes x (w-1) x (2 - 4/w), stay below this (measured
-// crossover at 4 ranks: between 512 KiB and 1 MiB).
-constexpr int64_t kCellsOneShotExtraBytes = 2 << 20;
+// shots 4 x bytes x (w-1)/w but cost one more NVLink crossing and a second round of waiting.  The
+// first wins up to this size (measured: 512 KiB 10.8 against 12.3 us at 4 ranks, 17.7 against 21.2 at
+// 8; 1 MiB 15.7 against 13.6 at 4 ranks and too large for the cell areas at 8).
+constexpr int64_t kCellsOneShotMaxBytes = 512 << 10;
 
 struct Peers {
   unsigned char* base[kMaxRanks];

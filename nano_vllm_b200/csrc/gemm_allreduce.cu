@@ -363,8 +363,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_allreduce_kernel(const __gri
 // How a problem is run.  bn: the smallest of 32 / 64 / 128 columns that leaves at most one tile per
 // thread block (128 wide otherwise).  one_shot: every rank pushes its partial of every tile to
 // every peer and sums for itself -- one NVLink crossing instead of two, (w-1) x the bytes; chosen
-// by the rule of the plain all-reduce (always at two ranks, at more while the extra bytes stay
-// under kCellsOneShotExtraBytes) where the cell area holds a region per tile and source.
+// by the rule of the plain all-reduce (always at two ranks, at more up to kCellsOneShotMaxBytes
+// of output) where the cell area holds a region per tile and source.
 // mode: 0 = that rule, 1 = one shot where it fits, 2 = two shots.  bn == 0: the shape or the cell
 // areas do not allow the kernel.
 struct Plan {
@@ -385,7 +385,7 @@ static Plan make_plan(int64_t m, int64_t n, int64_t k, int world, int64_t stage_
   const bool one_fits = tiles * world * cell_bytes <= stage_bytes;
   // two shots: a tile's 4-column groups are dealt out to the ranks in turn (8 groups at bn = 32)
   const bool two_fits = (world == 2 || world == 4 || world == 8) && tiles * cell_bytes <= stage_bytes;
-  const bool one_preferred = world == 2 || m * n * 2 * (world - 1) * (2 * world - 4) / world <= kCellsOneShotExtraBytes;
+  const bool one_preferred = world == 2 || m * n * 2 <= kCellsOneShotMaxBytes;
   if (one_fits && (mode == 1 || (mode == 0 && one_preferred) || !two_fits)) pl.one_shot = 1;
   else if (!two_fits) return pl;
   pl.bn = bn;

@@ -117,7 +117,8 @@ def test_all_reduce_protocol_choice_is_host_arithmetic(lib):
     assert protocol_for(4 << 20, 2, mb) == "one-shot"
     assert protocol_for(32 << 10, 8, mb) == "cells" and protocol_for(128 << 10, 8, mb) == "cells"
     assert protocol_for(512 << 10, 4, mb) == "cells" and protocol_for(1 << 20, 4, mb) == "cells-two-shot"
-    assert protocol_for(512 << 10, 8, mb) == "cells-two-shot" and protocol_for(2 << 20, 4, mb) == "cells-two-shot"
+    assert protocol_for(512 << 10, 8, mb) == "cells" and protocol_for(1 << 20, 8, mb) == "cells-two-shot"
+    assert protocol_for(2 << 20, 4, mb) == "cells-two-shot" and protocol_for(2 << 20, 8, mb) == "cells-two-shot"
     assert protocol_for(2 << 20, 8, mb, forced=3) == "two-shot" and protocol_for(6 << 20, 4, mb) == "two-shot"
     assert protocol_for((2 << 20) + 6, 8, mb) == "cells-two-shot"    # a ragged tail is fine for cells
     assert protocol_for(2 << 20, 8, mb, forced=2) == "one-shot"
